@@ -7,7 +7,7 @@
 //   PRISM_ACT_TANH       tanh(z)
 //   PRISM_ACT_SIGMOID    1 / (1 + exp(-z))
 // and the gated product out[i] = x[i] * act(g[i]) * c, with the gate g in float32 (a projection's float32
-// result) whatever the dtype of x and out.
+// result) whatever the dtype of x and out; one gate entry may cover `group` neighbouring columns (a gate per head).
 // Input and output rows may have strides of their own (the output may be a column block of a wider buffer).
 #include "common.cuh"
 #include "vec.cuh"
@@ -78,29 +78,31 @@ static int launch_activation(const void* x, long long xs, void* out, long long o
 
 template <typename T, int ACT>
 __global__ void gated_product_kernel(const T* __restrict__ x_in, long long x_stride, const float* __restrict__ g_in,
-                                     long long g_stride, T* __restrict__ out, long long out_stride, int cols, float c) {
+                                     long long g_stride, T* __restrict__ out, long long out_stride, int cols, float c,
+                                     int group) {
     pdl_trigger();
     pdl_wait();
     const T* x = pdl_fresh(x_in) + (size_t)blockIdx.y * x_stride;
     const float* g = pdl_fresh(g_in) + (size_t)blockIdx.y * g_stride;
     T* o = out + (size_t)blockIdx.y * out_stride;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < cols; i += gridDim.x * blockDim.x)
-        o[i] = from_float<T>(to_float(x[i]) * activate<ACT>(g[i]) * c);
+        o[i] = from_float<T>(to_float(x[i]) * activate<ACT>(g[i / group]) * c);
 }
 
 }  // namespace prism
 
-// out = x * act(gate) * c; x and out [rows, cols] of `dtype`, gate float32, each with a row stride of its own.
+// out = x * act(gate) * c; x and out [rows, cols] of `dtype`, gate [rows, cols / group] float32, each with a row stride
+// of its own.
 // act: PRISM_ACT_SIGMOID or PRISM_ACT_SILU.
 PRISM_EXPORT int prism_gated_product(const void* x, long long x_stride, const float* gate, long long gate_stride, void* out,
-                                     long long out_stride, int dtype, int rows, int cols, int act, float c,
+                                     long long out_stride, int dtype, int rows, int cols, int act, float c, int group,
                                      cudaStream_t stream) {
     if (rows <= 0 || cols <= 0) return 0;
-    if (rows > 65535 || (act != PRISM_ACT_SIGMOID && act != PRISM_ACT_SILU)) return (int)cudaErrorInvalidValue;
+    if (group < 1 || rows > 65535 || (act != PRISM_ACT_SIGMOID && act != PRISM_ACT_SILU)) return (int)cudaErrorInvalidValue;
     dim3 grid((cols + 255) / 256, rows);
 #define PRISM_GP(TT, A)                                                                                              \
     return (int)prism::launch_kernel(prism::gated_product_kernel<TT, A>, grid, dim3(256), 0, stream, (const TT*)x,    \
-                                     x_stride, gate, gate_stride, (TT*)out, out_stride, cols, c)
+                                     x_stride, gate, gate_stride, (TT*)out, out_stride, cols, c, group)
     if (dtype == PRISM_DTYPE_BF16) {
         if (act == PRISM_ACT_SIGMOID) PRISM_GP(__nv_bfloat16, PRISM_ACT_SIGMOID);
         PRISM_GP(__nv_bfloat16, PRISM_ACT_SILU);

@@ -1,0 +1,283 @@
+// Mixture of experts: every token goes through `top` of E small gated feed-forward layers, chosen by a router.
+//   scores s = sigmoid(z) (or softmax(z)) of the float32 router logits z [T, E]; the `top` largest are taken (the
+//   lower index wins a tie); the weight of a choice is its score, optionally divided by the sum of the chosen.
+// The (token, choice) pairs are sorted by expert on the device, so that each expert's rows are one stretch:
+//   prism_moe_route    top-k per token; counts[e] rows per expert, and each pair's rank among its expert's rows
+//   prism_moe_place    offs = prefix sums of counts; per sorted row: its token, its weight, and where its result goes
+//   prism_moe_gemm     grouped product over the sorted rows, expert by expert, no host knowledge of the counts:
+//                      (dual)   hidden[p] = act(Wg[e] a_p) * (Wu[e] a_p),  a_p = x[token[p]] * (weight[p] or 1)
+//                      (single) y[dst[p]] = Wd[e] hidden[p] * (weight[p] or 1)
+// The weight multiplies the expert's input (scale_in) or its output.  dst[p] = choice * T + token: the results of a
+// token's choices land in `top` planes [top, T, W] that the next norm adds up in float32, in a fixed order.
+// CUDA-core FFMA with float32 accumulation, k ascending inside one thread: a row's result does not depend on the
+// batch around it.  bf16 operands are widened exactly, so the sums equal a tensor-core product's up to their order.
+#include "common.cuh"
+
+namespace prism {
+
+__device__ __forceinline__ float moe_sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float moe_act(float z, int act) {
+    if (act == 0) return z / (1.f + expf(-z));                                                      // silu
+    if (act == 1) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));   // gelu_tanh
+    return fmaxf(z, 0.f);                                                                             // relu
+}
+
+// One warp per token.  logits [T, E] float32 (row stride ls).  sel_e, sel_w, sel_rank [T, top].
+__global__ void moe_route_kernel(const float* __restrict__ logits_in, long long ls, int T, int E, int top, int softmax,
+                                 int renorm, int* __restrict__ counts, int* __restrict__ sel_e, float* __restrict__ sel_w,
+                                 int* __restrict__ sel_rank) {
+    pdl_trigger();
+    pdl_wait();
+    const float* logits = pdl_fresh(logits_in);
+    extern __shared__ float sc[];                       // [warps][E]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= T) return;
+    float* s = sc + (size_t)warp * E;
+    const float* z = logits + (size_t)t * ls;
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+    mx = warp_max(mx);
+    float den = 0.f;
+    for (int e = lane; e < E; e += 32) {
+        const float v = softmax ? expf(z[e] - mx) : moe_sigmoid(z[e]);
+        s[e] = v;
+        den += v;
+    }
+    den = warp_sum(den);
+    __syncwarp();
+    float chosen = 0.f;
+    for (int j = 0; j < top; ++j) {
+        float best = -INFINITY;
+        int at = E;
+        for (int e = lane; e < E; e += 32)
+            if (s[e] > best) { best = s[e]; at = e; }           // ascending e: the lowest index of equal scores
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (at >= E) at = 0;                                   // every score NaN: keep the indices legal
+        const float w = softmax ? best / den : best;
+        chosen += w;
+        if (lane == 0) {
+            sel_e[(size_t)t * top + j] = at;
+            sel_w[(size_t)t * top + j] = w;
+            sel_rank[(size_t)t * top + j] = atomicAdd(counts + at, 1);
+            s[at] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    if (renorm && lane == 0)
+        for (int j = 0; j < top; ++j) sel_w[(size_t)t * top + j] /= chosen;
+}
+
+// offs [E + 1]; row_tok, row_w, row_dst [T top] in sorted order.
+__global__ void moe_place_kernel(const int* __restrict__ counts_in, const int* __restrict__ sel_e_in,
+                                 const float* __restrict__ sel_w_in, const int* __restrict__ sel_rank_in, int T, int E, int top,
+                                 int* __restrict__ offs, int* __restrict__ row_tok, float* __restrict__ row_w,
+                                 int* __restrict__ row_dst) {
+    pdl_trigger();
+    pdl_wait();
+    const int* counts = pdl_fresh(counts_in);
+    const int* sel_e = pdl_fresh(sel_e_in);
+    const float* sel_w = pdl_fresh(sel_w_in);
+    const int* sel_rank = pdl_fresh(sel_rank_in);
+    extern __shared__ int so[];                          // [E + 1]
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int e = 0; e < E; ++e) {
+            so[e] = acc;
+            acc += counts[e];
+        }
+        so[E] = acc;
+    }
+    __syncthreads();
+    if (blockIdx.x == 0)
+        for (int e = threadIdx.x; e <= E; e += blockDim.x) offs[e] = so[e];
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * top) return;
+    const int t = i / top, j = i - t * top;
+    const int p = so[sel_e[i]] + sel_rank[i];
+    row_tok[p] = t;
+    row_w[p] = sel_w[i];
+    row_dst[p] = j * T + t;
+}
+
+// Grouped product over the sorted rows.  A [*, K] of AT (row stride lda): DUAL reads row row_tok[p] (times row_w[p] with
+// scale_in, rounded to AT), single reads row p.  W [E, N (x2 for DUAL: the gate's rows, then the up's), K] of AT.
+// DUAL: out [T top, N] of AT at row p.  single: out [top T, N] float32 at row row_dst[p] (times row_w[p] without
+// scale_in).  grid (N tiles, row tiles): row tile i belongs to the expert whose tiles of BM rows cover it.
+template <typename AT, bool DUAL, int BM, int BN, int BK, int TM, int TN>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+moe_gemm_kernel(const AT* __restrict__ A_in, long long lda, const AT* __restrict__ W, const int* __restrict__ offs_in,
+                const int* __restrict__ row_tok_in, const float* __restrict__ row_w_in, const int* __restrict__ row_dst_in, int E,
+                int N, int K, int scale_in, int act, void* __restrict__ out, long long ldo) {
+    pdl_trigger();
+    pdl_wait();
+    const AT* A = pdl_fresh(A_in);
+    const int* offs = pdl_fresh(offs_in);
+    const int* row_tok = pdl_fresh(row_tok_in);
+    const float* row_w = pdl_fresh(row_w_in);
+    const int* row_dst = pdl_fresh(row_dst_in);
+    constexpr int THREADS = (BM / TM) * (BN / TN);
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Ws[BK][BN + 4];
+    __shared__ float Us[DUAL ? BK : 1][BN + 4];
+    __shared__ int rows_src[BM];
+    __shared__ float rows_w[BM];
+    __shared__ int tile_info[3];
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        int idx = blockIdx.y, e = 0, found = -1, m0 = 0;
+        for (; e < E; ++e) {
+            const int c = offs[e + 1] - offs[e];
+            const int tiles = (c + BM - 1) / BM;
+            if (idx < tiles) {
+                found = e;
+                m0 = offs[e] + idx * BM;
+                break;
+            }
+            idx -= tiles;
+        }
+        tile_info[0] = found;
+        tile_info[1] = m0;
+        tile_info[2] = found >= 0 ? offs[found + 1] : 0;
+    }
+    __syncthreads();
+    const int e = tile_info[0], m0 = tile_info[1], mend = tile_info[2];
+    if (e < 0) return;
+    for (int r = tid; r < BM; r += THREADS) {
+        const int p = m0 + r;
+        rows_src[r] = p < mend ? (DUAL ? row_tok[p] : p) : -1;
+        rows_w[r] = p < mend ? row_w[p] : 0.f;
+    }
+    __syncthreads();
+    const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+    const int n0 = blockIdx.x * BN;
+    const AT* We = W + (size_t)e * (DUAL ? 2 : 1) * N * K;
+    const AT* Wu = We + (size_t)N * K;
+    float acc[TM][TN], acu[DUAL ? TM : 1][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            acc[i][j] = 0.f;
+            if (DUAL) acu[i][j] = 0.f;
+        }
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        for (int idx = tid; idx < BM * BK; idx += THREADS) {
+            const int r = idx / BK, c = idx % BK;
+            const int src = rows_src[r];
+            float v = 0.f;
+            if (src >= 0 && k0 + c < K) {
+                v = to_float(A[(size_t)src * lda + k0 + c]);
+                if (DUAL && scale_in) v = to_float(from_float<AT>(v * rows_w[r]));
+            }
+            As[c][r] = v;
+        }
+        for (int idx = tid; idx < BN * BK; idx += THREADS) {
+            const int r = idx / BK, c = idx % BK;
+            const bool ok = n0 + r < N && k0 + c < K;
+            Ws[c][r] = ok ? to_float(We[(size_t)(n0 + r) * K + k0 + c]) : 0.f;
+            if (DUAL) Us[c][r] = ok ? to_float(Wu[(size_t)(n0 + r) * K + k0 + c]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a[TM], b[TN], u[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) {
+                b[j] = Ws[kk][tx * TN + j];
+                if (DUAL) u[j] = Us[kk][tx * TN + j];
+            }
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) {
+                    acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                    if (DUAL) acu[i][j] = fmaf(a[i], u[j], acu[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int r = ty * TM + i;
+        const int p = m0 + r;
+        if (p >= mend) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int n = n0 + tx * TN + j;
+            if (n >= N) continue;
+            if (DUAL) {
+                reinterpret_cast<AT*>(out)[(size_t)p * ldo + n] = from_float<AT>(moe_act(acc[i][j], act) * acu[i][j]);
+            } else {
+                reinterpret_cast<float*>(out)[(size_t)row_dst[p] * ldo + n] = scale_in ? acc[i][j] : acc[i][j] * rows_w[r];
+            }
+        }
+    }
+}
+
+}  // namespace prism
+
+// logits [T, E] float32; counts [E] int32, zero before the call; sel_e, sel_rank int32 and sel_w float32 [T, top].
+PRISM_EXPORT int prism_moe_route(const float* logits, long long logits_stride, int T, int E, int top, int softmax, int renorm,
+                                 int* counts, int* sel_e, float* sel_w, int* sel_rank, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (E < 1 || top < 1 || top > E) return (int)cudaErrorInvalidValue;
+    const int warps = 4;
+    const size_t smem = (size_t)warps * E * sizeof(float);
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    auto kern = prism::moe_route_kernel;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return (int)prism::launch_kernel(kern, dim3((T + warps - 1) / warps), dim3(32 * warps), smem, stream, logits, logits_stride,
+                                     T, E, top, softmax, renorm, counts, sel_e, sel_w, sel_rank);
+}
+
+PRISM_EXPORT int prism_moe_place(const int* counts, const int* sel_e, const float* sel_w, const int* sel_rank, int T, int E,
+                                 int top, int* offs, int* row_tok, float* row_w, int* row_dst, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const size_t smem = (size_t)(E + 1) * sizeof(int);
+    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    return (int)prism::launch_kernel(prism::moe_place_kernel, dim3((T * top + 255) / 256), dim3(256), smem, stream, counts, sel_e,
+                                     sel_w, sel_rank, T, E, top, offs, row_tok, row_w, row_dst);
+}
+
+// rows = T top sorted rows.  dual 1: a [T, K], w [E, 2 N, K], out [rows, N] of dtype; dual 0: a [rows, K], w [E, N, K],
+// out [rows, N] float32 (written at row_dst).  act: 0 silu, 1 gelu_tanh, 2 relu.
+PRISM_EXPORT int prism_moe_gemm(const void* a, long long lda, const void* w, int dtype, const int* offs, const int* row_tok,
+                                const float* row_w, const int* row_dst, int rows, int E, int N, int K, int dual, int scale_in,
+                                int act, void* out, long long ldo, cudaStream_t stream) {
+    if (rows <= 0 || N <= 0) return 0;
+    if (E < 1 || K < 1) return (int)cudaErrorInvalidValue;
+#define PRISM_MG(AT, D, BM, BN, BK, TM, TN)                                                                              \
+    do {                                                                                                                 \
+        long long tiles = (rows + BM - 1) / BM + E;                                                                      \
+        if (tiles > rows) tiles = rows;                                                                                  \
+        if (tiles > 65535) return (int)cudaErrorInvalidValue;                                                            \
+        dim3 grid((N + BN - 1) / BN, (unsigned)tiles);                                                                   \
+        return (int)prism::launch_kernel(prism::moe_gemm_kernel<AT, D, BM, BN, BK, TM, TN>, grid,                         \
+                                         dim3((BM / TM) * (BN / TN)), 0, stream, (const AT*)a, lda, (const AT*)w, offs,   \
+                                         row_tok, row_w, row_dst, E, N, K, scale_in, act, out, ldo);                     \
+    } while (0)
+    const bool few = rows <= 16 * E / 2 || rows <= 64;       // most experts see under a tile's worth of rows
+    if (dtype == PRISM_DTYPE_BF16) {
+        if (dual) {
+            if (few) PRISM_MG(__nv_bfloat16, true, 16, 32, 32, 1, 2);
+            PRISM_MG(__nv_bfloat16, true, 64, 32, 16, 4, 2);
+        }
+        if (few) PRISM_MG(__nv_bfloat16, false, 16, 64, 32, 1, 4);
+        PRISM_MG(__nv_bfloat16, false, 64, 64, 16, 4, 4);
+    }
+    if (dual) {
+        if (few) PRISM_MG(float, true, 16, 32, 32, 1, 2);
+        PRISM_MG(float, true, 64, 32, 16, 4, 2);
+    }
+    if (few) PRISM_MG(float, false, 16, 64, 32, 1, 4);
+    PRISM_MG(float, false, 64, 64, 16, 4, 4);
+#undef PRISM_MG
+}

@@ -3,6 +3,8 @@
 //
 //   delta rule with a scalar decay (SCAN_DELTA), per token with unit-length q, k and g, beta in (0, 1):
 //       S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q          (the read-out sees this token's write)
+//   delta rule with one decay per key channel (SCAN_CHANNEL), w a vector over the key channels:
+//       S <- diag(w) S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
 //   decayed outer-product sum with a bonus for the current token (SCAN_BONUS), w, u vectors over the key channels:
 //       o = (S + diag(u) k v^T)^T r;   S <- diag(w) S + k v^T                    (the read-out sees S before the write)
 //
@@ -24,6 +26,7 @@
 
 #define PRISM_SCAN_DELTA 0
 #define PRISM_SCAN_BONUS 1
+#define PRISM_SCAN_CHANNEL 2
 
 namespace prism {
 
@@ -81,6 +84,10 @@ __global__ void conv_unit_gates_kernel(const float* __restrict__ proj_in, long l
         for (int d = lane; d < dk; d += 32) out[hh * dk + d] = row[d] * inv;
     }
     for (int c = 2 * G * dk + threadIdx.x; c < C; c += blockDim.x) out[c] = y[c];
+    if (a_log == nullptr) {            // the decay is formed elsewhere (one per key channel): bg [T, H] holds beta alone
+        for (int h = threadIdx.x; h < H; h += blockDim.x) bg[(size_t)t * H + h] = sigmoid_f(proj[(size_t)t * ps + ob + h]);
+        return;
+    }
     for (int h = threadIdx.x; h < H; h += blockDim.x) {
         bg[(size_t)t * 2 * H + h] = sigmoid_f(proj[(size_t)t * ps + ob + h]);
         const float dt = softplus_f(proj[(size_t)t * ps + oa + h] + load_param(dt_bias, dt_bf16, h));
@@ -135,15 +142,21 @@ __global__ void decay_from_exponent_kernel(float* __restrict__ w, long long ws, 
         row[c] = expf(-expf(row[c] + load_param(w0, w0_bf16, c)));
 }
 
-// decay[t][n] = exp(-exp(sum_r tanh(low[t][r]) w2t[r][n] + w0[n])): the per-channel decay from the low-rank product's
-// first half, in one launch (tanh, the second product, the offset and both exponentials), all float32.  A CTA takes
-// 128 channels and sixteen tokens, so that every weight it reads serves sixteen tokens (whose tanh values sit side
-// by side in shared memory: four 128-bit loads per weight); w2t is the second matrix transposed, [R, N], so that
-// neighbouring threads read neighbouring floats.
+// out[t][n] = epi(sum_r inner(low[t][r]) w2t[r][n] + b[n]): the second half of a low-rank product with what follows it,
+// in one launch and float32 throughout.  inner: tanh (1) or nothing (0).  epi:
+//   PRISM_LR_EXPEXP    exp(-exp(z))                          a per-channel decay from its double exponent
+//   PRISM_LR_SOFTPLUS  exp(-exp(alog[n / per]) softplus(z))  a per-channel decay with one rate per group of `per` channels
+//   PRISM_LR_SIGMOID   sigmoid(z)                            a gate
+// b may be null.  A CTA takes 128 channels and sixteen tokens, so that every weight it reads serves sixteen tokens
+// (whose inner values sit side by side in shared memory: four 128-bit loads per weight); w2t is the second matrix
+// transposed, [R, N], so that neighbouring threads read neighbouring floats.
+#define PRISM_LR_EXPEXP 0
+#define PRISM_LR_SOFTPLUS 1
+#define PRISM_LR_SIGMOID 2
 constexpr int LRD_TOK = 16;
 __global__ void lowrank_decay_kernel(const float* __restrict__ low_in, long long ls, int R, const float* __restrict__ w2t,
                                      const void* __restrict__ w0, int w0_bf16, int N, int T, float* __restrict__ out,
-                                     long long os) {
+                                     long long os, int inner, int epi, const void* __restrict__ alog, int alog_bf16, int per) {
     pdl_trigger();
     pdl_wait();
     const float* low = pdl_fresh(low_in);
@@ -151,7 +164,8 @@ __global__ void lowrank_decay_kernel(const float* __restrict__ low_in, long long
     const int t0 = blockIdx.y * LRD_TOK, n = blockIdx.x * blockDim.x + threadIdx.x;
     for (int i = threadIdx.x; i < LRD_TOK * R; i += blockDim.x) {
         const int j = i / R, r = i - j * R;            // neighbouring threads read neighbouring entries of a token's row
-        s[r * LRD_TOK + j] = t0 + j < T ? tanhf(low[(size_t)(t0 + j) * ls + r]) : 0.f;
+        const float v = t0 + j < T ? low[(size_t)(t0 + j) * ls + r] : 0.f;
+        s[r * LRD_TOK + j] = inner ? tanhf(v) : v;
     }
     __syncthreads();
     if (n >= N) return;
@@ -169,18 +183,24 @@ __global__ void lowrank_decay_kernel(const float* __restrict__ low_in, long long
             acc[j + 3] += w * t4.w;
         }
     }
-    const float b = load_param(w0, w0_bf16, n);
+    const float b = w0 != nullptr ? load_param(w0, w0_bf16, n) : 0.f;
+    const float rate = epi == PRISM_LR_SOFTPLUS ? expf(load_param(alog, alog_bf16, n / per)) : 0.f;
 #pragma unroll
     for (int j = 0; j < LRD_TOK; ++j)
-        if (t0 + j < T) out[(size_t)(t0 + j) * os + n] = expf(-expf(acc[j] + b));
+        if (t0 + j < T) {
+            const float z = acc[j] + b;
+            out[(size_t)(t0 + j) * os + n] = epi == PRISM_LR_EXPEXP ? expf(-expf(z))
+                                             : epi == PRISM_LR_SOFTPLUS ? expf(-rate * softplus_f(z)) : sigmoid_f(z);
+        }
 }
 
-// out[t][h dv + c] = o[t][h][c] / sqrt(mean_c(o[t][h]^2) + eps) * weight[widx] * silu(gate[t][h dv + c]) * scale,
+// out[t][h dv + c] = o[t][h][c] / sqrt(mean_c(o[t][h]^2) + eps) * weight[widx] * act(gate[t][h dv + c]) * scale,
+// act silu, or sigmoid (gate_sigmoid; the gate may then hold the sigmoid already: gate_sigmoid 2),
 // widx = c (one weight for all heads) or h dv + c (per_head_weight).  One warp per (token, head).
 template <typename T>
 __global__ void headnorm_gate_kernel(const float* __restrict__ o_in, const float* __restrict__ gate_in, long long gs,
                                      const void* __restrict__ weight, int weight_bf16, int per_head_weight, float eps,
-                                     float scale, int Ttot, int H, int dv, T* __restrict__ out, long long os) {
+                                     float scale, int Ttot, int H, int dv, T* __restrict__ out, long long os, int gate_sigmoid) {
     pdl_trigger();
     pdl_wait();
     const float* o = pdl_fresh(o_in);
@@ -196,7 +216,8 @@ __global__ void headnorm_gate_kernel(const float* __restrict__ o_in, const float
     const float inv = 1.f / sqrtf(ss / (float)dv + eps);
     for (int c = lane; c < dv; c += 32) {
         const float wv = load_param(weight, weight_bf16, per_head_weight ? (size_t)h * dv + c : (size_t)c);
-        const float g = silu_f(gate[(size_t)t * gs + (size_t)h * dv + c]);
+        const float gz = gate[(size_t)t * gs + (size_t)h * dv + c];
+        const float g = gate_sigmoid == 2 ? gz : (gate_sigmoid ? sigmoid_f(gz) : silu_f(gz));
         out[(size_t)t * os + (size_t)h * dv + c] = from_float<T>(row[c] * inv * wv * g * scale);
     }
 }
@@ -212,6 +233,7 @@ __global__ void headnorm_gate_kernel(const float* __restrict__ o_in, const float
 //                bg [T, 2 H]: beta | g.
 //   SCAN_BONUS:  r at qo + h dk, k at ko + h dk, v at vo + h dv, the decay's exponent ww [T, H dk] (row stride ws)
 //                with w = exp(-exp(ww + w0)) formed in shared memory, w0 [H dk], bonus u [H dk].
+//   SCAN_CHANNEL: q, k, v as for SCAN_DELTA; the decay itself in ww [T, H dk] (row stride ws); bg [T, H]: beta.
 // ---------------------------------------------------------------------------------------------------------
 struct ScanArgs {
     const float* x;          // q | k | v (or r | k | v) rows
@@ -254,7 +276,7 @@ __global__ void scan_kernel(const ScanArgs a) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float sm[];
-    constexpr int NV = MODE == PRISM_SCAN_BONUS ? 3 : 2;       // vectors over the key channels per token
+    constexpr int NV = MODE == PRISM_SCAN_DELTA ? 2 : 3;       // vectors over the key channels per token
     constexpr int Q = R / 4;                                   // quads of rows a thread owns
     const int h = blockIdx.x, seg = blockIdx.y, col0 = blockIdx.z * a.cols;
     const int s0 = a.seg_start[seg], qlen = a.seg_start[seg + 1] - s0;
@@ -301,7 +323,7 @@ __global__ void scan_kernel(const ScanArgs a) {
         float* dst0 = sm + (size_t)buf * TB * per_tok;
         const int unit = a.vec ? 4 : 1;
         const int nk = (dk + unit - 1) / unit, nc = (ncols + unit - 1) / unit;     // pieces per vector
-        const size_t head_q = (size_t)(MODE == PRISM_SCAN_DELTA ? kvh : h) * dk;
+        const size_t head_q = (size_t)(MODE == PRISM_SCAN_BONUS ? h : kvh) * dk;
         for (int tt = 0; tt < nb; ++tt) {
             const size_t t = (size_t)(s0 + b0 + tt);
             const float* xr = x + t * a.xs;
@@ -309,12 +331,14 @@ __global__ void scan_kernel(const ScanArgs a) {
             for (int c = lane; c < nk; c += 32) {
                 cp_async_f(dst + c * unit, xr + a.qo + head_q + c * unit, unit);
                 cp_async_f(dst + dkp + c * unit, xr + a.ko + head_q + c * unit, unit);
-                if (MODE == PRISM_SCAN_BONUS) cp_async_f(dst + 2 * dkp + c * unit, ww + t * a.ws + (size_t)h * dk + c * unit, unit);
+                if (MODE != PRISM_SCAN_DELTA) cp_async_f(dst + 2 * dkp + c * unit, ww + t * a.ws + (size_t)h * dk + c * unit, unit);
             }
             for (int c = lane; c < nc; c += 32)
                 cp_async_f(dst + NV * dkp + c * unit, xr + a.vo + (size_t)h * dv + col0 + c * unit, unit);
             if (MODE == PRISM_SCAN_DELTA && lane < 2)                                // beta, then g
                 cp_async_f(dst + NV * dkp + a.colsp + lane, bg + t * 2 * a.H + (size_t)lane * a.H + h, 1);
+            if (MODE == PRISM_SCAN_CHANNEL && lane == 0)                             // beta
+                cp_async_f(dst + NV * dkp + a.colsp, bg + t * a.H + h, 1);
         }
         cp_async_commit();
     };
@@ -403,6 +427,41 @@ __global__ void scan_kernel(const ScanArgs a) {
                     o2 += S[4 * m + 2] * qq.z;
                     o3 += S[4 * m + 3] * qq.w;
                 }
+            } else if (MODE == PRISM_SCAN_CHANNEL) {
+                const float* wd = f2 + dkp;
+                const float* vv = wd + dkp;
+                const float beta = vv[a.colsp];
+                float k0 = 0.f, k1 = 0.f, k2 = 0.f, k3 = 0.f;
+                float4 kq[Q];
+#pragma unroll
+                for (int m = 0; m < Q; ++m) {
+                    const int i = 4 * (part + L * m);
+                    kq[m] = *reinterpret_cast<const float4*>(f2 + i);
+                    const float4 w4 = *reinterpret_cast<const float4*>(wd + i);
+                    S[4 * m] *= w4.x;
+                    S[4 * m + 1] *= w4.y;
+                    S[4 * m + 2] *= w4.z;
+                    S[4 * m + 3] *= w4.w;
+                    k0 += S[4 * m] * kq[m].x;
+                    k1 += S[4 * m + 1] * kq[m].y;
+                    k2 += S[4 * m + 2] * kq[m].z;
+                    k3 += S[4 * m + 3] * kq[m].w;
+                }
+                float ks = (k0 + k1) + (k2 + k3);
+                ks = column_sum<L>(ks);
+                const float uu = beta * (vv[lc] - ks);
+#pragma unroll
+                for (int m = 0; m < Q; ++m) {
+                    const float4 qq = *reinterpret_cast<const float4*>(f1 + 4 * (part + L * m));
+                    S[4 * m] += kq[m].x * uu;
+                    S[4 * m + 1] += kq[m].y * uu;
+                    S[4 * m + 2] += kq[m].z * uu;
+                    S[4 * m + 3] += kq[m].w * uu;
+                    o0 += S[4 * m] * qq.x;
+                    o1 += S[4 * m + 1] * qq.y;
+                    o2 += S[4 * m + 2] * qq.z;
+                    o3 += S[4 * m + 3] * qq.w;
+                }
             } else {
                 const float* wd = f2 + dkp;
                 const float v = wd[dkp + lc];
@@ -445,7 +504,7 @@ __global__ void scan_kernel(const ScanArgs a) {
 
 template <int MODE, int R, int L>
 static int launch_scan(const ScanArgs& a, int S, cudaStream_t stream) {
-    const int per_tok = (MODE == PRISM_SCAN_BONUS ? 3 : 2) * a.dkp + a.colsp + 4;
+    const int per_tok = (MODE == PRISM_SCAN_DELTA ? 2 : 3) * a.dkp + a.colsp + 4;
     const size_t smem = ((size_t)3 * a.TB * per_tok + (MODE == PRISM_SCAN_BONUS ? a.dkp : 0)) * sizeof(float);
     auto kern = scan_kernel<MODE, R, L>;
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
@@ -503,21 +562,25 @@ PRISM_EXPORT int prism_decay_from_exponent(float* w, long long w_stride, const v
                                      w_stride, w0, w0_dtype == PRISM_DTYPE_BF16, A);
 }
 
-// low [T, R] float32 (row stride free), w2t [R, N] float32, w0 [N]; out [T, N] float32.
+// low [T, R] float32 (row stride free), w2t [R, N] float32, w0 [N] or null; out [T, N] float32; inner 1: tanh of low;
+// epi PRISM_LR_*; alog [N / per] for PRISM_LR_SOFTPLUS.
 PRISM_EXPORT int prism_lowrank_decay(const float* low, long long low_stride, int R, const float* w2t, const void* w0,
-                                     int w0_dtype, int N, int T, float* out, long long out_stride, cudaStream_t stream) {
+                                     int w0_dtype, int N, int T, float* out, long long out_stride, int inner, int epi,
+                                     const void* alog, int alog_dtype, int per, cudaStream_t stream) {
+    if (epi == PRISM_LR_SOFTPLUS && (alog == nullptr || per < 1)) return (int)cudaErrorInvalidValue;
     if (T <= 0 || N <= 0) return 0;
     const size_t smem = (size_t)prism::LRD_TOK * R * sizeof(float);
     if (R < 1 || smem > 200 * 1024 || (T + prism::LRD_TOK - 1) / prism::LRD_TOK > 65535) return (int)cudaErrorInvalidValue;
     auto kern = prism::lowrank_decay_kernel;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return (int)prism::launch_kernel(kern, dim3((N + 127) / 128, (T + prism::LRD_TOK - 1) / prism::LRD_TOK), dim3(128), smem,
-                                     stream, low, low_stride, R, w2t, w0, w0_dtype == PRISM_DTYPE_BF16, N, T, out, out_stride);
+                                     stream, low, low_stride, R, w2t, w0, w0_dtype == PRISM_DTYPE_BF16, N, T, out, out_stride, inner, epi, alog,
+                                     alog_dtype == PRISM_DTYPE_BF16, per < 1 ? 1 : per);
 }
 
 PRISM_EXPORT int prism_headnorm_gate(const float* o, const float* gate, long long gate_stride, const void* weight,
                                      int weight_dtype, int per_head_weight, float eps, float scale, int T, int H, int dv,
-                                     void* out, int out_dtype, long long out_stride, cudaStream_t stream) {
+                                     void* out, int out_dtype, long long out_stride, int gate_sigmoid, cudaStream_t stream) {
     if (T <= 0 || H <= 0 || dv <= 0) return 0;
     const int warps = 4;
     const long long total = (long long)T * H;
@@ -526,9 +589,9 @@ PRISM_EXPORT int prism_headnorm_gate(const float* o, const float* gate, long lon
     if (out_dtype == PRISM_DTYPE_BF16)
         return (int)prism::launch_kernel(prism::headnorm_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), 0, stream, o,
                                          gate, gate_stride, weight, wb, per_head_weight, eps, scale, T, H, dv,
-                                         (__nv_bfloat16*)out, out_stride);
+                                         (__nv_bfloat16*)out, out_stride, gate_sigmoid);
     return (int)prism::launch_kernel(prism::headnorm_gate_kernel<float>, dim3(blocks), dim3(warps * 32), 0, stream, o, gate,
-                                     gate_stride, weight, wb, per_head_weight, eps, scale, T, H, dv, (float*)out, out_stride);
+                                     gate_stride, weight, wb, per_head_weight, eps, scale, T, H, dv, (float*)out, out_stride, gate_sigmoid);
 }
 
 // mode PRISM_SCAN_*; state [slots, H, dv, dk] float32; out [T, H, dv] float32; rep: heads per q/k head (DELTA).
@@ -564,8 +627,8 @@ PRISM_EXPORT int prism_recurrent_scan(int mode, const float* x, long long x_stri
     a.colsp = (cols + 3) / 4 * 4;
     a.vec = dk % 4 == 0 && dv % 4 == 0 && cols % 4 == 0 && x_stride % 4 == 0 && qo % 4 == 0 && ko % 4 == 0 && vo % 4 == 0 &&
             (uintptr_t)x % 16 == 0 && (uintptr_t)state % 16 == 0 &&
-            (mode != PRISM_SCAN_BONUS || (ww_stride % 4 == 0 && (uintptr_t)ww % 16 == 0));
-    const int per_tok = (mode == PRISM_SCAN_BONUS ? 3 : 2) * a.dkp + a.colsp + 4;
+            (mode == PRISM_SCAN_DELTA || (ww_stride % 4 == 0 && (uintptr_t)ww % 16 == 0));
+    const int per_tok = (mode == PRISM_SCAN_DELTA ? 2 : 3) * a.dkp + a.colsp + 4;
     int tb = (24 * 1024 / 4) / per_tok;
     tb = tb < 1 ? 1 : (tb > 16 ? 16 : tb);
     a.TB = tb > max_q_len ? (max_q_len < 1 ? 1 : max_q_len) : tb;      // a decode step stages one token, and CTAs are small
@@ -581,6 +644,7 @@ PRISM_EXPORT int prism_recurrent_scan(int mode, const float* x, long long x_stri
     } while (0)
     if (mode == PRISM_SCAN_DELTA) PRISM_SCAN(PRISM_SCAN_DELTA);
     if (mode == PRISM_SCAN_BONUS) PRISM_SCAN(PRISM_SCAN_BONUS);
+    if (mode == PRISM_SCAN_CHANNEL) PRISM_SCAN(PRISM_SCAN_CHANNEL);
 #undef PRISM_SCAN
     return (int)cudaErrorInvalidValue;
 }

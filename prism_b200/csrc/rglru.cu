@@ -1,0 +1,222 @@
+// Real-gated linear recurrent unit: a recurrence with one float32 number of state per channel,
+//     S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t,      a_t = exp(-c r_t softplus(lam)),
+// whose gates r and i are sigmoids of block-diagonal products of u (the channels are split into equal blocks,
+// each with a square matrix for r and one for i).  Three kernels:
+//   * prism_causal_conv   u = conv(x) + bias: the short causal convolution over time per channel (its last taps - 1
+//     inputs per request are state too; a step of single tokens moves that tail up itself);
+//   * prism_block_gates   both block-diagonal products with the recurrence's coefficients as epilogue: from u it
+//     writes a and sqrt(1 - a^2) i u, float32 throughout (CUDA cores, k ascending inside one thread, so a row's
+//     result does not depend on the batch);
+//   * prism_rglru_scan    the recurrence itself from and into the request's state slot, token after token, times
+//     the other branch's activation, rounded once to the compute dtype.
+#include "common.cuh"
+
+namespace prism {
+
+__device__ __forceinline__ float rg_sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float rg_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float rg_gelu_tanh(float z) {
+    return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// out[t][c] = bias[c] + sum_j taps[c][K-1-j] x[t-j][c]; x [T, *] float32 with row stride xs; tail [slots, K-1, C].
+__global__ void causal_conv_kernel(const float* __restrict__ x_in, long long xs, const void* __restrict__ taps, int taps_bf16,
+                                   const void* __restrict__ bias, int bias_bf16, int K, int C, float* tail,
+                                   const int* __restrict__ tok_seg, const int* __restrict__ seg_start,
+                                   const int* __restrict__ slots, float* __restrict__ out, long long os, int move_tail) {
+    pdl_trigger();
+    pdl_wait();
+    const float* x = pdl_fresh(x_in);
+    const int t = blockIdx.x, seg = tok_seg[t];
+    const int i = t - seg_start[seg];
+    float* tl = tail + (size_t)slots[seg] * (K - 1) * C;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        float acc = bias != nullptr ? load_param(bias, bias_bf16, c) : 0.f;
+        for (int j = K - 1; j >= 0; --j) {
+            const int src = i - j;
+            const float v = src >= 0 ? x[(size_t)(t - j) * xs + c] : tl[(size_t)(K - 1 + src) * C + c];
+            acc += load_param(taps, taps_bf16, (size_t)c * K + (K - 1 - j)) * v;
+        }
+        out[(size_t)t * os + c] = acc;
+        if (move_tail && K > 1) {          // one token per request: this thread is the only reader of its channel's tail
+            for (int r = 0; r + 2 < K; ++r) tl[(size_t)r * C + c] = tl[(size_t)(r + 1) * C + c];
+            tl[(size_t)(K - 2) * C + c] = x[(size_t)t * xs + c];
+        }
+    }
+}
+
+// Block b of channels [b bs, (b + 1) bs): r = sigmoid(Wr[b] u_b + br[b]), i = sigmoid(Wi[b] u_b + bi[b]);
+// a = exp(-c r softplus(lam)), g = sqrt(1 - a^2) i u.  Wr, Wi [blocks, bs, bs] ([out, in]); grid (bs tiles, token tiles,
+// blocks).  1 - a^2 is formed as -expm1(2 log a), which keeps its leading digits where a is close to 1.
+template <typename WT, int BM, int BN, int BK, int TM, int TN>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+block_gates_kernel(const float* __restrict__ u_in, long long us, const WT* __restrict__ Wr, const WT* __restrict__ Wi,
+                   const void* __restrict__ br, const void* __restrict__ bi, int b_bf16, const void* __restrict__ lam,
+                   int lam_bf16, float cdecay, int T, int bs, float* __restrict__ a_out, float* __restrict__ g_out,
+                   long long os) {
+    pdl_trigger();
+    pdl_wait();
+    const float* u = pdl_fresh(u_in);
+    constexpr int THREADS = (BM / TM) * (BN / TN);
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Rs[BK][BN + 4];
+    __shared__ float Is[BK][BN + 4];
+    const int tid = threadIdx.x;
+    const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+    const int blk = blockIdx.z, m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const size_t wbase = (size_t)blk * bs * bs;
+    const float* ub = u + (size_t)blk * bs;
+    float ar[TM][TN], ai[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) ar[i][j] = ai[i][j] = 0.f;
+    for (int k0 = 0; k0 < bs; k0 += BK) {
+        for (int idx = tid; idx < BM * BK; idx += THREADS) {
+            const int r = idx / BK, c = idx % BK;
+            As[c][r] = (m0 + r < T && k0 + c < bs) ? ub[(size_t)(m0 + r) * us + k0 + c] : 0.f;
+        }
+        for (int idx = tid; idx < BN * BK; idx += THREADS) {
+            const int r = idx / BK, c = idx % BK;
+            const bool ok = n0 + r < bs && k0 + c < bs;
+            const size_t at = wbase + (size_t)(n0 + r) * bs + k0 + c;
+            Rs[c][r] = ok ? to_float(Wr[at]) : 0.f;
+            Is[c][r] = ok ? to_float(Wi[at]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a[TM], r[TN], ii[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) {
+                r[j] = Rs[kk][tx * TN + j];
+                ii[j] = Is[kk][tx * TN + j];
+            }
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) {
+                    ar[i][j] = fmaf(a[i], r[j], ar[i][j]);
+                    ai[i][j] = fmaf(a[i], ii[j], ai[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int m = m0 + ty * TM + i;
+        if (m >= T) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int n = n0 + tx * TN + j;
+            if (n >= bs) continue;
+            const size_t ch = (size_t)blk * bs + n;
+            const float r = rg_sigmoid(ar[i][j] + load_param(br, b_bf16, ch));
+            const float gi = rg_sigmoid(ai[i][j] + load_param(bi, b_bf16, ch));
+            const float loga = -cdecay * r * rg_softplus(load_param(lam, lam_bf16, ch));
+            a_out[(size_t)m * os + ch] = expf(loga);
+            g_out[(size_t)m * os + ch] = sqrtf(-expm1f(2.f * loga)) * gi * ub[(size_t)m * us + n];
+        }
+    }
+}
+
+// S <- a S + g per channel, token after token of each request of the step; out = S * gelu_tanh(y) (act 1) or S * y.
+// grid (channel blocks, segments); a thread owns a channel.  The loads of the next tokens do not depend on S, so
+// they are issued four tokens ahead of the chain of multiply-adds.
+template <typename T>
+__global__ void rglru_scan_kernel(const float* __restrict__ a_in, const float* __restrict__ g_in, long long as,
+                                  const float* __restrict__ y_in, long long ys, float* __restrict__ state,
+                                  const int* __restrict__ seg_start, const int* __restrict__ slots, int C, int act,
+                                  T* __restrict__ out, long long os) {
+    pdl_trigger();
+    pdl_wait();
+    const float* a = pdl_fresh(a_in);
+    const float* g = pdl_fresh(g_in);
+    const float* y = pdl_fresh(y_in);
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int seg = blockIdx.y, s0 = seg_start[seg], s1 = seg_start[seg + 1];
+    float* st = state + (size_t)slots[seg] * C + c;
+    float S = *st;
+    int t = s0;
+    for (; t + 4 <= s1; t += 4) {
+        float av[4], gv[4], yv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            av[j] = a[(size_t)(t + j) * as + c];
+            gv[j] = g[(size_t)(t + j) * as + c];
+            yv[j] = y[(size_t)(t + j) * ys + c];
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            S = fmaf(av[j], S, gv[j]);
+            out[(size_t)(t + j) * os + c] = from_float<T>(S * (act ? rg_gelu_tanh(yv[j]) : yv[j]));
+        }
+    }
+    for (; t < s1; ++t) {
+        S = fmaf(a[(size_t)t * as + c], S, g[(size_t)t * as + c]);
+        const float yv = y[(size_t)t * ys + c];
+        out[(size_t)t * os + c] = from_float<T>(S * (act ? rg_gelu_tanh(yv) : yv));
+    }
+    *st = S;
+}
+
+}  // namespace prism
+
+PRISM_EXPORT int prism_causal_conv(const float* x, long long x_stride, const void* taps, int taps_dtype, const void* bias,
+                                   int bias_dtype, int K, int C, float* tail, const int* tok_seg, const int* seg_start,
+                                   const int* slots, int T, float* out, long long out_stride, int move_tail,
+                                   cudaStream_t stream) {
+    if (T <= 0 || C <= 0) return 0;
+    if (K < 1) return (int)cudaErrorInvalidValue;
+    const int threads = 128;
+    int gy = (C + threads - 1) / threads;
+    if (gy > 64) gy = 64;
+    return (int)prism::launch_kernel(prism::causal_conv_kernel, dim3(T, gy), dim3(threads), 0, stream, x, x_stride, taps,
+                                     taps_dtype == PRISM_DTYPE_BF16, bias, bias_dtype == PRISM_DTYPE_BF16, K, C, tail, tok_seg,
+                                     seg_start, slots, out, out_stride, move_tail);
+}
+
+// u [T, blocks * bs] float32 (row stride u_stride); wr, wi [blocks, bs, bs] of w_dtype; br, bi [blocks * bs] of b_dtype;
+// lam [blocks * bs]; a_out, g_out [T, blocks * bs] float32 with row stride out_stride.
+PRISM_EXPORT int prism_block_gates(const float* u, long long u_stride, const void* wr, const void* wi, int w_dtype,
+                                   const void* br, const void* bi, int b_dtype, const void* lam, int lam_dtype, float cdecay,
+                                   int T, int blocks, int bs, float* a_out, float* g_out, long long out_stride,
+                                   cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (blocks < 1 || bs < 1 || blocks > 65535) return (int)cudaErrorInvalidValue;
+    const int bb = b_dtype == PRISM_DTYPE_BF16, lb = lam_dtype == PRISM_DTYPE_BF16;
+#define PRISM_BG(WT, BM, BK, TM)                                                                                        \
+    do {                                                                                                                \
+        dim3 grid((bs + 31) / 32, (T + BM - 1) / BM, blocks);                                                           \
+        if (grid.y > 65535) return (int)cudaErrorInvalidValue;                                                          \
+        return (int)prism::launch_kernel(prism::block_gates_kernel<WT, BM, 32, BK, TM, 2>, grid, dim3((BM / TM) * 16), 0, \
+                                         stream, u, u_stride, (const WT*)wr, (const WT*)wi, br, bi, bb, lam, lb, cdecay, T, \
+                                         bs, a_out, g_out, out_stride);                                                 \
+    } while (0)
+    if (w_dtype == PRISM_DTYPE_BF16) {
+        if (T <= 16) PRISM_BG(__nv_bfloat16, 16, 32, 1);
+        PRISM_BG(__nv_bfloat16, 64, 16, 4);
+    }
+    if (T <= 16) PRISM_BG(float, 16, 32, 1);
+    PRISM_BG(float, 64, 16, 4);
+#undef PRISM_BG
+}
+
+// a, g [T, C] float32 (one row stride), y [T, C] float32 (row stride y_stride), state [slots, C] float32,
+// out [T, C] of out_dtype; act 1: gelu_tanh(y), 0: y as it is.
+PRISM_EXPORT int prism_rglru_scan(const float* a, const float* g, long long ag_stride, const float* y, long long y_stride,
+                                  float* state, const int* seg_start, const int* slots, int S, int C, int act, void* out,
+                                  int out_dtype, long long out_stride, cudaStream_t stream) {
+    if (S <= 0 || C <= 0) return 0;
+    if (S > 65535) return (int)cudaErrorInvalidValue;
+    const int threads = (long long)S * C >= 148 * 256 ? 128 : 32;       // few requests: more, smaller CTAs
+    dim3 grid((C + threads - 1) / threads, S);
+    if (out_dtype == PRISM_DTYPE_BF16)
+        return (int)prism::launch_kernel(prism::rglru_scan_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, a, g, ag_stride,
+                                         y, y_stride, state, seg_start, slots, C, act, (__nv_bfloat16*)out, out_stride);
+    return (int)prism::launch_kernel(prism::rglru_scan_kernel<float>, grid, dim3(threads), 0, stream, a, g, ag_stride, y,
+                                     y_stride, state, seg_start, slots, C, act, (float*)out, out_stride);
+}

@@ -96,16 +96,23 @@ class _Sig:
     prism_attention_masked_bf16 = [_p, _ll, _i, _p, _ll, _p, _ll, _i, _p, _ll, _i, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i,
                                    _i, _i, _i, _i, _i, _f, _p, _i, _i, _i, _p, _p, _p, _p]
     prism_scale_add_rmsnorm = [_p, _f, _p, _i, _i, _ll, _p, _i, _f, _p, _i, _i, _i, _p]
-    prism_gated_product = [_p, _ll, _p, _ll, _p, _ll, _i, _i, _i, _i, _f, _p]
+    prism_gated_product = [_p, _ll, _p, _ll, _p, _ll, _i, _i, _i, _i, _f, _i, _p]
     prism_qk_norm_rope_store = [_p, _p, _p, _ll, _p, _i, _p, _i, _f, _p, _i, _p, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i,
-                                _i, _i, _i, _i, _p, _p]
+                                _i, _i, _i, _i, _p, _i, _i, _p]
     prism_conv_unit_gates = [_p, _ll, _i, _i, _p, _i, _i, _p, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p, _p, _i, _p]
     prism_state_tail = [_p, _ll, _i, _p, _i, _p, _p, _i, _p]
     prism_shift_mix = [_p, _i, _p, _p, _i, _i, _p, _p, _p, _i, _p, _i, _ll, _i, _p]
-    prism_headnorm_gate = [_p, _p, _ll, _p, _i, _i, _f, _f, _i, _i, _i, _p, _i, _ll, _p]
+    prism_headnorm_gate = [_p, _p, _ll, _p, _i, _i, _f, _f, _i, _i, _i, _p, _i, _ll, _i, _p]
     prism_recurrent_scan = [_i, _p, _ll, _ll, _ll, _ll, _p, _p, _ll, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _i, _p]
     prism_decay_from_exponent = [_p, _ll, _p, _i, _i, _i, _p]
-    prism_lowrank_decay = [_p, _ll, _i, _p, _p, _i, _i, _i, _p, _ll, _p]
+    prism_lowrank_decay = [_p, _ll, _i, _p, _p, _i, _i, _i, _p, _ll, _i, _i, _p, _i, _i, _p]
+    prism_moe_route = [_p, _ll, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p]
+    prism_moe_place = [_p, _p, _p, _p, _i, _i, _i, _p, _p, _p, _p, _p]
+    prism_moe_gemm = [_p, _ll, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _ll, _p]
+    prism_hyper_norm = [_p, _ll, _p, _ll, _p, _i, _i, _ll, _p, _i, _p, _i, _p, _i, _i, _p, _i, _f, _i, _p, _i, _p, _i, _i, _p]
+    prism_causal_conv = [_p, _ll, _p, _i, _p, _i, _i, _i, _p, _p, _p, _p, _i, _p, _ll, _i, _p]
+    prism_block_gates = [_p, _ll, _p, _p, _i, _p, _p, _i, _p, _i, _f, _i, _i, _i, _p, _p, _ll, _p]
+    prism_rglru_scan = [_p, _p, _ll, _p, _ll, _p, _p, _p, _i, _i, _i, _p, _i, _ll, _p]
     prism_cache_store = [_p, _ll, _p, _i, _i, _p, _ll, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p]
     prism_latent_kv_store = [_p, _ll, _p, _i, _f, _i, _i, _i, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p, _i, _p, _i,
                              _p, _ll, _p]
@@ -1495,41 +1502,54 @@ def scale_add_rmsnorm(x: torch.Tensor, alpha: float, delta: Optional[torch.Tenso
 
 
 def gated_product(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, kind: str = "sigmoid", scale: float = 1.0):
-    """``out = x * act(gate) * scale``; ``x`` and ``out`` ``[rows, cols]`` in the compute dtype, ``gate`` float32,
-    each with a row stride of its own; ``kind``: ``sigmoid`` or ``silu``."""
+    """``out = x * act(gate) * scale``; ``x`` and ``out`` ``[rows, cols]`` in the compute dtype, ``gate`` float32
+    ``[rows, cols / group]`` (one gate entry for ``group`` neighbouring columns: a gate per head), each with a row
+    stride of its own; ``kind``: ``sigmoid`` or ``silu``."""
     _cuda(x, gate, out)
     rows, cols = x.shape
-    assert gate.dtype == torch.float32 and gate.shape == x.shape and out.shape == x.shape and out.dtype == x.dtype
+    assert gate.dtype == torch.float32 and gate.shape[0] == rows and out.shape == x.shape and out.dtype == x.dtype
     assert x.stride(1) == 1 and gate.stride(1) == 1 and out.stride(1) == 1
+    assert gate.shape[1] > 0 and cols % gate.shape[1] == 0
     _check(lib().prism_gated_product(_ptr(x), x.stride(0), _ptr(gate), gate.stride(0), _ptr(out), out.stride(0), _dt(x),
-                                     rows, cols, ACTIVATIONS[kind], float(scale), _stream()), "gated_product")
+                                     rows, cols, ACTIVATIONS[kind], float(scale), cols // gate.shape[1], _stream()),
+           "gated_product")
 
 
-def qk_norm_rope_store(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_weight: Optional[torch.Tensor],
-                       k_weight: Optional[torch.Tensor], eps: float, freq: Optional[torch.Tensor], rot: int,
-                       q_out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor, block_table: torch.Tensor,
-                       positions: torch.Tensor, tok_seg: torch.Tensor, num_pages: int, max_pos: int, err: torch.Tensor):
+def qk_norm_rope_store(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor],
+                       q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                       freq: Optional[torch.Tensor], rot: int, q_out: torch.Tensor, k_plane: Optional[torch.Tensor],
+                       v_plane: Optional[torch.Tensor], block_table: torch.Tensor, positions: torch.Tensor,
+                       tok_seg: torch.Tensor, num_pages: int, max_pos: int, err: torch.Tensor, whole: bool = False,
+                       halves: bool = False, nkv: Optional[int] = None):
     """From float32 column blocks ``q [T, nh * dk]``, ``k [T, nkv * dk]``, ``v [T, nkv * dv]`` of one product (one
-    row stride): RMS norm of every q and k head with ``q_weight`` / ``k_weight`` (``[dk]``, None: no norm), rotation
-    of the first ``rot`` entries in interleaved pairs by ``position * freq[i]``; q into ``q_out [T, nh, dk]``, k and v
-    into their cache planes at the token's slot."""
+    row stride): RMS norm of every q and k head with ``q_weight`` / ``k_weight`` (``[dk]``, None: no norm) - or,
+    with ``whole``, of the whole projection at once (weights ``[nh * dk]`` and ``[nkv * dk]``); rotation of the
+    first ``rot`` entries by ``position * freq[i]``, in interleaved pairs or (``halves``) entry i with entry
+    ``i + rot / 2``; q into ``q_out [T, nh, dk]``, k and v into their cache planes at the token's slot.  ``k``, ``v``
+    and the planes None: the layer has no keys and values of its own, only q is made."""
     _cuda(q, k, v, q_weight, k_weight, freq, q_out, k_plane, v_plane, block_table, positions, tok_seg)
     T, nh, dk = q_out.shape
-    nkv, dv = k_plane.shape[2], v_plane.shape[3]
-    assert q.dtype == k.dtype == v.dtype == torch.float32 and q.stride(1) == k.stride(1) == v.stride(1) == 1
-    assert q.shape == (T, nh * dk) and k.shape == (T, nkv * dk) and v.shape == (T, nkv * dv)
-    assert T == 1 or q.stride(0) == k.stride(0) == v.stride(0)
-    assert q_out.is_contiguous() and k_plane.is_contiguous() and v_plane.is_contiguous()
-    assert k_plane.dtype == q_out.dtype == v_plane.dtype and k_plane.shape[3] == dk and k_plane.shape[:3] == v_plane.shape[:3]
+    assert q.dtype == torch.float32 and q.stride(1) == 1 and q.shape == (T, nh * dk) and q_out.is_contiguous()
+    if k_plane is None:
+        assert k is None and v is None and v_plane is None
+        nkv, dv, P = int(nkv or 1), 1, 1
+        k = v = q                       # never read
+    else:
+        nkv, dv, P = k_plane.shape[2], v_plane.shape[3], k_plane.shape[1]
+        assert k.dtype == v.dtype == torch.float32 and k.stride(1) == v.stride(1) == 1
+        assert k.shape == (T, nkv * dk) and v.shape == (T, nkv * dv)
+        assert T == 1 or q.stride(0) == k.stride(0) == v.stride(0)
+        assert k_plane.is_contiguous() and v_plane.is_contiguous()
+        assert k_plane.dtype == q_out.dtype == v_plane.dtype and k_plane.shape[3] == dk and k_plane.shape[:3] == v_plane.shape[:3]
     if rot:
         assert freq.dtype == torch.float32 and freq.shape == (rot // 2,) and freq.is_contiguous()
-    for w in (q_weight, k_weight):
-        assert w is None or (w.shape == (dk,) and w.is_contiguous())
+    for w, n in ((q_weight, nh), (k_weight, nkv)):
+        assert w is None or (w.shape == ((n * dk,) if whole else (dk,)) and w.is_contiguous())
     _check(lib().prism_qk_norm_rope_store(
         _ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(q_weight), F32 if q_weight is None else _dt(q_weight), _ptr(k_weight),
         F32 if k_weight is None else _dt(k_weight), float(eps), _ptr(freq), int(rot), _ptr(q_out), _ptr(k_plane),
         _ptr(v_plane), _dt(q_out), _ptr(block_table), block_table.shape[1], _ptr(positions), _ptr(tok_seg), T, nh, nkv, dk,
-        dv, k_plane.shape[1], num_pages, int(max_pos), _ptr(err), _stream()), "qk_norm_rope_store")
+        dv, P, num_pages, int(max_pos), _ptr(err), 1 if whole else 0, 1 if halves else 0, _stream()), "qk_norm_rope_store")
 
 
 def conv_unit_gates(proj: torch.Tensor, b_off: int, a_off: int, taps: torch.Tensor, tail: torch.Tensor,
@@ -1546,10 +1566,15 @@ def conv_unit_gates(proj: torch.Tensor, b_off: int, a_off: int, taps: torch.Tens
     C, K = taps.shape
     assert C == 2 * G * dk + H * dv and proj.dtype == torch.float32 and proj.stride(1) == 1 and taps.is_contiguous()
     assert tail.dtype == torch.float32 and tail.is_contiguous() and tuple(tail.shape[1:]) == (max(K - 1, 0), C)
-    assert qkv.shape == (T, C) and qkv.is_contiguous() and bg.shape == (T, 2 * H) and bg.is_contiguous()
-    assert qkv.dtype == torch.float32 and bg.dtype == torch.float32 and a_log.shape == (H,) and dt_bias.shape == (H,)
+    assert qkv.shape == (T, C) and qkv.is_contiguous() and bg.is_contiguous()
+    assert qkv.dtype == torch.float32 and bg.dtype == torch.float32
+    if a_log is None:               # the decay is formed elsewhere (one per key channel): bg holds beta alone
+        assert bg.shape == (T, H)
+    else:
+        assert bg.shape == (T, 2 * H) and a_log.shape == (H,) and dt_bias.shape == (H,)
     _check(lib().prism_conv_unit_gates(_ptr(proj), proj.stride(0), int(b_off), int(a_off), _ptr(taps), _dt(taps), K,
-                                       _ptr(tail), _ptr(a_log), _dt(a_log), _ptr(dt_bias), _dt(dt_bias), _ptr(ctx.tok_seg),
+                                       _ptr(tail), _ptr(a_log), F32 if a_log is None else _dt(a_log), _ptr(dt_bias),
+                                       F32 if dt_bias is None else _dt(dt_bias), _ptr(ctx.tok_seg),
                                        _ptr(ctx.seg_start), _ptr(ctx.state_slots), T, G, H, dk, dv, float(unit_eps),
                                        _ptr(qkv), _ptr(bg), 1 if move_tail else 0, _stream()), "conv_unit_gates")
 
@@ -1583,8 +1608,10 @@ def shift_mix(x: torch.Tensor, prev: torch.Tensor, mu: torch.Tensor, ctx, out: t
            "shift_mix")
 
 
-def headnorm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, scale: float, out: torch.Tensor):
-    """``out[t, h] = o[t, h] / rms(o[t, h]) * weight * silu(gate[t, h]) * scale``; ``o [T, H, dv]`` float32, ``gate
+def headnorm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, scale: float, out: torch.Tensor,
+                  gate_act: str = "silu"):
+    """``out[t, h] = o[t, h] / rms(o[t, h]) * weight * act(gate[t, h]) * scale``, ``gate_act``: ``silu``, ``sigmoid`` or
+    ``none`` (the gate holds the factor itself); ``o [T, H, dv]`` float32, ``gate
     [T, H * dv]`` float32 and ``out [T, H * dv]`` (compute dtype) with row strides of their own; ``weight [dv]`` (one
     for all heads) or ``[H * dv]``."""
     _cuda(o, gate, weight, out)
@@ -1594,10 +1621,11 @@ def headnorm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps
     assert weight.shape in ((dv,), (H * dv,))
     per_head = 1 if (weight.shape[0] == H * dv and H > 1) else 0
     _check(lib().prism_headnorm_gate(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), _dt(weight), per_head, float(eps),
-                                     float(scale), T, H, dv, _ptr(out), _dt(out), out.stride(0), _stream()), "headnorm_gate")
+                                     float(scale), T, H, dv, _ptr(out), _dt(out), out.stride(0),
+                                     {"silu": 0, "sigmoid": 1, "none": 2}[gate_act], _stream()), "headnorm_gate")
 
 
-SCAN_DELTA, SCAN_BONUS = 0, 1      # csrc/recurrent.cu: PRISM_SCAN_*
+SCAN_DELTA, SCAN_BONUS, SCAN_CHANNEL = 0, 1, 2      # csrc/recurrent.cu: PRISM_SCAN_*
 
 
 def recurrent_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, ctx, H: int,
@@ -1609,7 +1637,8 @@ def recurrent_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     one row stride - column blocks of one product, or products of their own.  ``SCAN_DELTA``: delta rule with ``bg
     [T, 2 H]`` (beta | scalar decay), ``rep`` heads share a q/k head.  ``SCAN_BONUS``: per-channel decay ``exp(-exp(ww
     + w0))`` (``ww [T, H * dk]``) and bonus ``u [H * dk]`` for the current token; ``decay_ready``: ``ww`` holds the decay
-    itself (``lowrank_decay``, ``decay_from_exponent``).  ``out [T, H, dv]`` float32."""
+    itself (``lowrank_decay``, ``decay_from_exponent``).  ``SCAN_CHANNEL``: delta rule whose decay is a vector over the
+    key channels, ``ww [T, H * dk]`` (the decay itself), with ``bg [T, H]`` (beta).  ``out [T, H, dv]`` float32."""
     _cuda(q, k, v, state, out, bg, ww, w0, u)
     T = q.shape[0]
     for t in (q, k, v):
@@ -1620,6 +1649,9 @@ def recurrent_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     assert out.shape == (T, H, dv) and out.is_contiguous() and out.dtype == torch.float32
     if mode == SCAN_DELTA:
         assert bg is not None and bg.shape == (T, 2 * H) and bg.is_contiguous() and bg.dtype == torch.float32
+    elif mode == SCAN_CHANNEL:
+        assert bg is not None and bg.shape == (T, H) and bg.is_contiguous() and bg.dtype == torch.float32
+        assert ww.dtype == torch.float32 and ww.shape == (T, H * dk) and ww.stride(1) == 1
     else:
         assert ww.dtype == torch.float32 and ww.shape == (T, H * dk) and ww.stride(1) == 1
         assert w0.numel() == H * dk and u.numel() == H * dk and w0.is_contiguous() and u.is_contiguous()
@@ -1634,18 +1666,27 @@ def recurrent_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
         "recurrent_scan")
 
 
-def lowrank_decay(low: torch.Tensor, w2t: torch.Tensor, w0: torch.Tensor, out: torch.Tensor):
-    """``out = exp(-exp(tanh(low) @ w2t + w0))``: the decayed-sum scan's per-channel decay from the first half of its
-    low-rank product, in one launch and in float32 throughout.  ``low [T, R]`` float32 (row stride free), ``w2t [R,
-    N]`` float32 (the second matrix, transposed), ``w0 [N]``, ``out [T, N]`` float32."""
-    _cuda(low, w2t, w0, out)
+LR_EXPEXP, LR_SOFTPLUS, LR_SIGMOID = 0, 1, 2      # csrc/recurrent.cu: PRISM_LR_*
+
+
+def lowrank_decay(low: torch.Tensor, w2t: torch.Tensor, w0: Optional[torch.Tensor], out: torch.Tensor, inner_tanh: bool = True,
+                  epilogue: int = LR_EXPEXP, rate_log: Optional[torch.Tensor] = None, per: int = 1):
+    """``out = epi(inner(low) @ w2t + w0)``: the second half of a low-rank product with what follows it, in one launch
+    and in float32 throughout.  ``inner``: tanh or nothing.  ``epilogue``: ``LR_EXPEXP`` ``exp(-exp(z))`` (a per-channel
+    decay from its double exponent), ``LR_SOFTPLUS`` ``exp(-exp(rate_log[n // per]) softplus(z))`` (a per-channel decay
+    with one rate per ``per`` channels), ``LR_SIGMOID`` (a gate).  ``low [T, R]`` float32 (row stride free), ``w2t [R,
+    N]`` float32 (the second matrix, transposed), ``w0 [N]`` or None, ``out [T, N]`` float32."""
+    _cuda(low, w2t, w0, out, rate_log)
     T, R = low.shape
     N = w2t.shape[1]
     assert low.dtype == torch.float32 and low.stride(1) == 1 and w2t.dtype == torch.float32 and w2t.is_contiguous()
-    assert w2t.shape[0] == R and w0.numel() == N and w0.is_contiguous() and out.shape == (T, N) and out.dtype == torch.float32
-    assert out.stride(1) == 1
-    _check(lib().prism_lowrank_decay(_ptr(low), low.stride(0), R, _ptr(w2t), _ptr(w0), _dt(w0), N, T, _ptr(out), out.stride(0),
-                                     _stream()), "lowrank_decay")
+    assert w2t.shape[0] == R and out.shape == (T, N) and out.dtype == torch.float32 and out.stride(1) == 1
+    assert w0 is None or (w0.numel() == N and w0.is_contiguous())
+    if epilogue == LR_SOFTPLUS:
+        assert rate_log is not None and rate_log.is_contiguous() and rate_log.numel() * per == N
+    _check(lib().prism_lowrank_decay(_ptr(low), low.stride(0), R, _ptr(w2t), _ptr(w0), F32 if w0 is None else _dt(w0), N, T,
+                                     _ptr(out), out.stride(0), 1 if inner_tanh else 0, int(epilogue), _ptr(rate_log),
+                                     F32 if rate_log is None else _dt(rate_log), int(per), _stream()), "lowrank_decay")
 
 
 def decay_from_exponent(ww: torch.Tensor, w0: torch.Tensor):
@@ -1655,3 +1696,131 @@ def decay_from_exponent(ww: torch.Tensor, w0: torch.Tensor):
     T, A = ww.shape
     assert ww.dtype == torch.float32 and ww.stride(1) == 1 and w0.numel() == A and w0.is_contiguous()
     _check(lib().prism_decay_from_exponent(_ptr(ww), ww.stride(0), _ptr(w0), _dt(w0), T, A, _stream()), "decay_from_exponent")
+
+
+def hyper_norm(x: torch.Tensor, streams: int, x_out: Optional[torch.Tensor], delta: Optional[torch.Tensor],
+               mix: Optional[torch.Tensor], out_w: Optional[torch.Tensor], in_w: Optional[torch.Tensor],
+               weight: Optional[torch.Tensor], eps: float, h: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None,
+               rms: bool = False):
+    """Hyper-connections around a sublayer, in one launch: the update that the previous sublayer left open, ``x_j <-
+    sum_i mix[i, j] x_i + out_w[j] delta`` for all ``streams`` copies at once, then the read-in ``u = sum_j in_w[j]
+    x_j`` and its norm ``h = norm(u) * weight`` (layer norm without bias, or RMS norm).  ``x``: ``[streams, T, W]``
+    float32, or ``[T, W]`` read as ``streams`` equal copies; ``x_out [streams, T, W]`` (may be ``x``; None: not written);
+    ``delta [T, W]`` or a stack ``[k, T, W]`` of partial sums, float32 or bf16 (None: nothing left open); ``mix`` None:
+    identity, ``out_w`` / ``in_w`` None: ones; ``weight`` None: the update alone.  ``rows``: only these tokens are
+    normed into ``h [len(rows), W]``, and the streams are not written."""
+    _cuda(x, x_out, delta, mix, out_w, in_w, weight, h, rows)
+    s = int(streams)
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.dim() in (2, 3)
+    T, W = x.shape[-2], x.shape[-1]
+    in_ss = T * W if x.dim() == 3 else 0
+    assert x.dim() == 2 or x.shape[0] == s
+    if x_out is not None:
+        assert x_out.dtype == torch.float32 and x_out.shape == (s, T, W) and x_out.is_contiguous()
+    nsplit = 0
+    if delta is not None:
+        assert delta.is_contiguous() and delta.shape[-2:] == (T, W)
+        nsplit = delta.shape[0] if delta.dim() == 3 else 1
+    for t, n in ((mix, s * s), (out_w, s), (in_w, s)):
+        assert t is None or (t.numel() == n and t.is_contiguous())
+    n = T if rows is None else rows.shape[0]
+    if weight is not None:
+        assert weight.shape == (W,) and weight.is_contiguous() and h.shape == (n, W) and h.is_contiguous()
+    dt = lambda t: F32 if t is None else _dt(t)
+    _check(lib().prism_hyper_norm(_ptr(x), in_ss, _ptr(x_out), T * W, _ptr(delta), dt(delta), nsplit, T * W, _ptr(mix), dt(mix),
+                                  _ptr(out_w), dt(out_w), _ptr(in_w), dt(in_w), s, _ptr(weight), dt(weight), float(eps),
+                                  1 if rms else 0, _ptr(h), dt(h), _ptr(rows), n, W, _stream()), "hyper_norm")
+
+
+def causal_conv(x: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], tail: torch.Tensor, ctx, out: torch.Tensor,
+                move_tail: bool = False):
+    """``out[t, c] = bias[c] + sum_j taps[c, K-1-j] x[t-j, c]``: a short causal convolution over time per channel,
+    float32; ``x [T, C]`` (row stride free), ``taps [C, K]`` (last column: the current token's), ``tail [slots, K - 1,
+    C]`` the request's last inputs before this step.  ``move_tail``: every request brings one token, and the kernel
+    moves the tail up itself (else ``state_tail`` follows)."""
+    _cuda(x, taps, bias, tail, out)
+    T = x.shape[0]
+    C, K = taps.shape
+    assert x.dtype == torch.float32 and x.stride(1) == 1 and x.shape[1] == C and taps.is_contiguous()
+    assert tail.dtype == torch.float32 and tail.is_contiguous() and tuple(tail.shape[1:]) == (max(K - 1, 0), C)
+    assert out.dtype == torch.float32 and out.shape == (T, C) and out.stride(1) == 1
+    assert bias is None or (bias.shape == (C,) and bias.is_contiguous())
+    _check(lib().prism_causal_conv(_ptr(x), x.stride(0), _ptr(taps), _dt(taps), _ptr(bias), F32 if bias is None else _dt(bias),
+                                   K, C, _ptr(tail), _ptr(ctx.tok_seg), _ptr(ctx.seg_start), _ptr(ctx.state_slots), T, _ptr(out),
+                                   out.stride(0), 1 if move_tail else 0, _stream()), "causal_conv")
+
+
+def block_gates(u: torch.Tensor, wr: torch.Tensor, wi: torch.Tensor, br: torch.Tensor, bi: torch.Tensor, lam: torch.Tensor,
+                cdecay: float, a_out: torch.Tensor, g_out: torch.Tensor):
+    """The gates of a real-gated linear recurrent unit and the recurrence's coefficients from them: per block b of
+    channels ``r = sigmoid(wr[b] u_b + br[b])``, ``i = sigmoid(wi[b] u_b + bi[b])``; ``a = exp(-cdecay r softplus(lam))``
+    into ``a_out`` and ``sqrt(1 - a^2) i u`` into ``g_out``.  ``u [T, blocks * bs]`` float32 (row stride free), ``wr``,
+    ``wi [blocks, bs, bs]`` ([out, in]); float32 arithmetic throughout."""
+    _cuda(u, wr, wi, br, bi, lam, a_out, g_out)
+    T, C = u.shape
+    blocks, bs = wr.shape[0], wr.shape[1]
+    assert u.dtype == torch.float32 and u.stride(1) == 1 and blocks * bs == C and wr.shape == wi.shape == (blocks, bs, bs)
+    assert wr.is_contiguous() and wi.is_contiguous() and wr.dtype == wi.dtype and br.dtype == bi.dtype
+    assert br.numel() == C and bi.numel() == C and lam.numel() == C and br.is_contiguous() and bi.is_contiguous() and lam.is_contiguous()
+    for t in (a_out, g_out):
+        assert t.dtype == torch.float32 and t.shape == (T, C) and t.stride(1) == 1 and t.stride(0) == a_out.stride(0)
+    _check(lib().prism_block_gates(_ptr(u), u.stride(0), _ptr(wr), _ptr(wi), _dt(wr), _ptr(br), _ptr(bi), _dt(br), _ptr(lam),
+                                   _dt(lam), float(cdecay), T, blocks, bs, _ptr(a_out), _ptr(g_out), a_out.stride(0), _stream()),
+           "block_gates")
+
+
+def rglru_scan(a: torch.Tensor, g: torch.Tensor, y: torch.Tensor, state: torch.Tensor, ctx, out: torch.Tensor,
+               gelu: bool = True):
+    """``S <- a S + g`` per channel, token after token of each request of the step, from and into ``state [slots, C]``
+    (float32); ``out = S * gelu_tanh(y)`` (or ``S * y``) in the compute dtype.  ``a``, ``g [T, C]`` float32 with one
+    row stride, ``y [T, C]`` float32 (row stride free)."""
+    _cuda(a, g, y, state, out)
+    T, C = a.shape
+    assert a.dtype == g.dtype == y.dtype == torch.float32 and a.stride(1) == g.stride(1) == y.stride(1) == 1
+    assert g.shape == (T, C) and y.shape == (T, C) and a.stride(0) == g.stride(0) and out.shape == (T, C) and out.stride(1) == 1
+    assert state.dtype == torch.float32 and state.is_contiguous() and state[0].numel() == C
+    _check(lib().prism_rglru_scan(_ptr(a), _ptr(g), a.stride(0), _ptr(y), y.stride(0), _ptr(state), _ptr(ctx.seg_start),
+                                  _ptr(ctx.state_slots), ctx.S, C, 1 if gelu else 0, _ptr(out), _dt(out), out.stride(0),
+                                  _stream()), "rglru_scan")
+
+
+MOE_ACTS = {"silu": 0, "gelu_tanh": 1, "relu": 2}      # csrc/moe.cu: moe_act
+
+
+def moe_feed_forward(ctx, x: torch.Tensor, logits: torch.Tensor, gate_up_w: torch.Tensor, down_w: torch.Tensor, top: int,
+                     softmax: bool = False, renorm: bool = False, scale_input: bool = True, act: str = "silu") -> torch.Tensor:
+    """Mixture of experts on the step's rows: ``x [T, W]`` (compute dtype), router ``logits [T, E]`` float32,
+    ``gate_up_w [E, 2 F, W]`` (an expert's gate rows, then its up rows), ``down_w [E, W, F]``.  Each token takes the
+    ``top`` experts with the largest scores (sigmoid of the logits, or their softmax); a choice's weight is its score
+    (``renorm``: over the sum of the chosen) and multiplies the expert's input (``scale_input``) or its output.
+    Returns float32 ``[top, T, W]``: one plane per choice, which the next norm adds up.  The rows are sorted by
+    expert on the device and run as grouped products; the host never learns the counts."""
+    _cuda(x, logits, gate_up_w, down_w)
+    T, W = x.shape
+    E, F2, _ = gate_up_w.shape
+    F = F2 // 2
+    assert logits.dtype == torch.float32 and logits.shape == (T, E) and logits.stride(1) == 1 and x.stride(1) == 1
+    assert gate_up_w.shape == (E, 2 * F, W) and down_w.shape == (E, W, F) and gate_up_w.is_contiguous() and down_w.is_contiguous()
+    assert gate_up_w.dtype == x.dtype and down_w.dtype == x.dtype and 1 <= top <= E
+    rows = T * top
+    dev = x.device
+    ints = torch.empty(E + (E + 1) + 4 * rows, dtype=torch.int32, device=dev)
+    counts, offs = ints[:E], ints[E:2 * E + 1]
+    o = 2 * E + 1
+    sel_e, sel_rank, row_tok, row_dst = (ints[o + i * rows:o + (i + 1) * rows] for i in range(4))
+    counts.zero_()
+    flt = torch.empty(2 * rows, dtype=torch.float32, device=dev)
+    sel_w, row_w = flt[:rows], flt[rows:]
+    L = lib()
+    _check(L.prism_moe_route(_ptr(logits), logits.stride(0), T, E, int(top), 1 if softmax else 0, 1 if renorm else 0,
+                             _ptr(counts), _ptr(sel_e), _ptr(sel_w), _ptr(sel_rank), _stream()), "moe_route")
+    _check(L.prism_moe_place(_ptr(counts), _ptr(sel_e), _ptr(sel_w), _ptr(sel_rank), T, E, int(top), _ptr(offs), _ptr(row_tok),
+                             _ptr(row_w), _ptr(row_dst), _stream()), "moe_place")
+    hidden = ctx.alloc((rows, F), x.dtype)
+    si = 1 if scale_input else 0
+    _check(L.prism_moe_gemm(_ptr(x), x.stride(0), _ptr(gate_up_w), _dt(x), _ptr(offs), _ptr(row_tok), _ptr(row_w), _ptr(row_dst),
+                            rows, E, F, W, 1, si, MOE_ACTS[act], _ptr(hidden), F, _stream()), "moe_gemm")
+    y = ctx.alloc((top, T, W), torch.float32)
+    _check(L.prism_moe_gemm(_ptr(hidden), F, _ptr(down_w), _dt(x), _ptr(offs), _ptr(row_tok), _ptr(row_w), _ptr(row_dst),
+                            rows, E, W, F, 0, si, 0, _ptr(y), W, _stream()), "moe_gemm")
+    return y

@@ -36,10 +36,12 @@ class GQAAttention(Mixer):
     mask; None: never (a plane that layers with different masks read).  ``keep_first``: under a window, the
     first ``keep_first`` positions of the sequence stay visible to every later query (at their true positions).
     ``qk_norm_eps``: every head of q and k is RMS-normed over ``head_dim`` before it is rotated, with one weight
-    vector for q and one for k that all heads share.  ``gate``: the concatenated heads are multiplied by
-    ``sigmoid(W_g h)`` before the output projection.  ``out_scale``: a constant on the layer's result (folded into
-    the gate).  A rotation in interleaved pairs (``RotaryParams.interleaved``), the query/key norm and the gate
-    work from the float32 result of the input projection.  ``names``: the tensors' names in the model file (keys
+    vector for q and one for k that all heads share; with ``qk_norm_whole`` the norm runs over the whole projection
+    instead (all heads of q, or of k, at once, with weights of that size).  ``gate``: the concatenated heads are
+    multiplied by ``sigmoid(W_g h)`` before the output projection; ``gate="head"``: one gate number per head.
+    ``sink_value``: a constant sink, the same for every head (0: one is added to the softmax's denominator).  ``out_scale``: a constant on the layer's result (folded into
+    the gate).  A rotation with rescaled frequencies (``rotary_scaled``), the query/key norm and the gate
+    work from the float32 result of the input projection; so may a layer without keys and values of its own.  ``names``: the tensors' names in the model file (keys
     q, k, v, o, q_b, k_b, v_b, o_b, sink, q_norm, k_norm, g)."""
 
     NAMES = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight",
@@ -52,7 +54,8 @@ class GQAAttention(Mixer):
                  position: Optional[PartSpec] = None, scale: Optional[float] = None,
                  v_head_dim: Optional[int] = None, chunk: Optional[int] = None, sink: bool = False,
                  own_kv: bool = True, cache_chunk="mask", names: Optional[dict] = None, keep_first: int = 0,
-                 qk_norm_eps: Optional[float] = None, gate: bool = False, out_scale: float = 1.0):
+                 qk_norm_eps: Optional[float] = None, gate=False, out_scale: float = 1.0, qk_norm_whole: bool = False,
+                 sink_value: Optional[float] = None):
         if num_heads % num_kv_heads:
             raise ConfigError(f"num_heads {num_heads} not divisible by num_kv_heads {num_kv_heads}")
         self.hidden_size, self.nh, self.nkv, self.hd = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
@@ -67,6 +70,9 @@ class GQAAttention(Mixer):
         if self.chunk is not None and self.window is not None:
             raise ConfigError("a layer's mask is a window or a chunk, not both")
         self.sink, self.own_kv = bool(sink), bool(own_kv)
+        self.sink_value = None if sink_value is None else float(sink_value)
+        if self.sink and self.sink_value is not None:
+            raise ConfigError("a layer's sink is learned or a constant, not both")
         self.cache_chunk = self.chunk if cache_chunk == "mask" else (None if cache_chunk is None else int(cache_chunk))
         self.names = dict(self.NAMES, **(names or {}))
         # what the fused rotate-and-store and the equal-size attention kernels do not cover goes the general way:
@@ -76,13 +82,16 @@ class GQAAttention(Mixer):
             raise ConfigError("keep_first: a number of first positions, kept visible behind a window")
         self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
         self.gate, self.out_scale = bool(gate), float(out_scale)
-        interleaved = bool(position and position.kind == "rotary_scaled" and position.args.get("interleaved", True))
-        # query/key norm, interleaved pairs and the gate read the input projection's float32 result
-        self.float32_projection = self.qk_norm_eps is not None or self.gate or interleaved
-        if self.float32_projection and (not self.own_kv or qkv_bias):
-            raise ConfigError("query/key norm, interleaved rotation and output gate: for layers with key and value "
-                              "projections of their own and without biases on them")
+        self.gate_per_head = gate == "head"
+        self.qk_norm_whole = bool(qk_norm_whole) and self.qk_norm_eps is not None
+        scaled = bool(position and position.kind == "rotary_scaled")
+        # query/key norm, a rotation from a table of rescaled frequencies and the gate read the input projection's
+        # float32 result
+        self.float32_projection = self.qk_norm_eps is not None or self.gate or scaled
+        if self.float32_projection and qkv_bias:
+            raise ConfigError("query/key norm, rescaled rotation and output gate: for layers without biases on q, k, v")
         self.general = (self.vhd != self.hd or self.chunk is not None or self.sink or not self.own_kv
+                        or self.sink_value is not None
                         or self.keep_first > 0 or self.float32_projection)
         self._own_in = self._own_out = True
         # the equal-size kernels keep a head's row in a warp's registers and rotate pairs; the general path takes
@@ -121,7 +130,7 @@ class GQAAttention(Mixer):
             w += [WeightSource(n["k"], (kvs, H)), WeightSource(n["v"], (vs, H))]
             b += [WeightSource(n["k_b"], (kvs,), "bias"), WeightSource(n["v_b"], (vs,), "bias")]
         if self.gate:
-            w.append(WeightSource(n["g"], (self.nh * self.vhd, H)))
+            w.append(WeightSource(n["g"], (self.nh if self.gate_per_head else self.nh * self.vhd, H)))
         return tuple(w), tuple(b) if self.qkv_bias else ()
 
     def _out_sources(self):
@@ -139,8 +148,10 @@ class GQAAttention(Mixer):
         if self.sink:
             ps.append(ParamSpec("sink", (WeightSource(self.names["sink"], (self.nh,), "bias"),)))
         if self.qk_norm_eps is not None:
-            ps.append(ParamSpec("q_norm", (WeightSource(self.names["q_norm"], (self.hd,), "norm"),)))
-            ps.append(ParamSpec("k_norm", (WeightSource(self.names["k_norm"], (self.hd,), "norm"),)))
+            nq, nk = (self.q_size, self.kv_size) if self.qk_norm_whole else (self.hd, self.hd)
+            ps.append(ParamSpec("q_norm", (WeightSource(self.names["q_norm"], (nq,), "norm"),)))
+            if self.own_kv:
+                ps.append(ParamSpec("k_norm", (WeightSource(self.names["k_norm"], (nk,), "norm"),)))
         if self._own_out:
             w, b = self._out_sources()
             ps.append(ParamSpec("o_w", w))
@@ -176,6 +187,8 @@ class GQAAttention(Mixer):
         # Said once, when the model is built, not found out from the step time: in bfloat16 the tensor-core
         # attention kernels take head sizes in steps of 16 up to 128 with up to 16 query heads per kv head; every
         # other shape runs on the shape-generic kernel (one warp per token and head), correct but far slower.
+        self.const_sink = (None if self.sink_value is None else
+                           torch.full((self.nh,), self.sink_value, dtype=torch.float32, device=self.device))
         if self.general:
             return
         if self.dtype == torch.bfloat16 and not ops.attention_bf16_shape_ok(self.hd, self.nh, self.nkv):
@@ -211,29 +224,38 @@ class GQAAttention(Mixer):
             ops.cache_store(qkv[:, qs:qs + kvs], cache.k, cache.block_table, ctx.positions, ctx.tok_seg, cache.num_pages,
                             ctx.max_positions, ctx.err, src2=qkv[:, qs + kvs:], plane2=cache.v)
         ops.masked_attention(ctx, q, out, cache.k, cache.v, cache.block_table, cache.num_pages, self.mask, self.scale,
-                             self.w.get("sink"))
+                             self._sink())
 
     def _forward_inner_f32(self, ctx, x, cache, out, proj):
-        """From the float32 projection ``[q | k | v | gate]``: one launch norms and rotates q and k and stores k
-        and v at the tokens' slots; attention under the mask; the gate (and ``out_scale``) on its way into ``out``."""
-        T, qs, kvs, vs = x.shape[0], self.q_size, self.kv_size, self.v_size
+        """From the float32 projection ``[q | k | v | gate]`` (``[q | gate]`` in a layer without keys and values of
+        its own): one launch norms and rotates q and k and stores k and v at the tokens' slots; attention under the
+        mask; the gate (and ``out_scale``) on its way into ``out``."""
+        T, qs = x.shape[0], self.q_size
+        kvs, vs = (self.kv_size, self.v_size) if self.own_kv else (0, 0)
         if proj is None:
             proj = ops.linear(x, self.w["qkv_w"], None, out_dtype=torch.float32)
         rot = self.position.rotary() if self.position is not None else None
-        if self.position is not None and (rot is None or (rot.rotary_dim and not rot.interleaved)):
-            raise ConfigError("with query/key norm or an output gate the attention part rotates interleaved pairs only")
+        if self.position is not None and rot is None:
+            raise ConfigError("with query/key norm or an output gate the attention part takes a rotary position encoding")
         q = ctx.alloc((T, self.nh, self.hd), ctx.dtype)
-        ops.qk_norm_rope_store(proj[:, :qs], proj[:, qs:qs + kvs], proj[:, qs + kvs:qs + kvs + vs], self.w.get("q_norm"),
-                               self.w.get("k_norm"), self.qk_norm_eps or 0.0, rot.inv_freq if rot and rot.rotary_dim else None,
-                               rot.rotary_dim if rot else 0, q, cache.k, cache.v, cache.block_table, ctx.positions,
-                               ctx.tok_seg, cache.num_pages, ctx.max_positions, ctx.err)
+        own = self.own_kv
+        ops.qk_norm_rope_store(proj[:, :qs], proj[:, qs:qs + kvs] if own else None,
+                               proj[:, qs + kvs:qs + kvs + vs] if own else None, self.w.get("q_norm"),
+                               self.w.get("k_norm") if own else None, self.qk_norm_eps or 0.0,
+                               rot.inv_freq if rot and rot.rotary_dim else None, rot.rotary_dim if rot else 0, q,
+                               cache.k if own else None, cache.v if own else None, cache.block_table, ctx.positions,
+                               ctx.tok_seg, cache.num_pages, ctx.max_positions, ctx.err, whole=self.qk_norm_whole,
+                               halves=bool(rot and not rot.interleaved), nkv=self.nkv)
         attn = ctx.alloc((T, self.nh * self.vhd), ctx.dtype) if self.gate else out
         ops.masked_attention(ctx, q, attn, cache.k, cache.v, cache.block_table, cache.num_pages, self.mask, self.scale,
-                             self.w.get("sink"))
+                             self._sink())
         if self.gate:
             ops.gated_product(attn, proj[:, qs + kvs + vs:], out, "sigmoid", self.out_scale)
         elif self.out_scale != 1.0:
             out.mul_(self.out_scale)
+
+    def _sink(self):
+        return self.w.get("sink") if self.sink else self.const_sink
 
     def forward(self, ctx, x, cache):
         if self.general:

@@ -35,7 +35,7 @@ from typing import Callable, Dict, List, Optional, Tuple
 class WeightSource:
     """One tensor of the model file: its name relative to the part's prefix,
     its shape, and how random-weights mode draws it
-    (``matrix`` | ``bias`` | ``norm``).  ``absolute``: the name is the file's
+    (``matrix`` | ``bias`` | ``norm`` | ``eye``: a square matrix near the identity).  ``absolute``: the name is the file's
     full name already (a tensor that another part has handed over)."""
     name: str
     shape: Tuple[int, ...]
@@ -125,6 +125,16 @@ class RotaryParams:
     inv_freq: object          # torch.Tensor [rotary_dim // 2] float32
     rotary_dim: int
     interleaved: bool = False # pairs (2i, 2i + 1) instead of (i, i + rotary_dim / 2)
+
+
+@dataclass
+class StreamUpdate:
+    """A sublayer's result that a block with several residual streams has left open: ``delta`` (``[T, W]`` or a stack
+    of partial sums) together with the weights that spread it over the streams, ``x_j <- sum_i mix[i, j] x_i +
+    out[j] delta``.  The next norm carries the update out in the launch that reads the streams anyway."""
+    delta: object
+    mix: object
+    out: object
 
 
 @dataclass(frozen=True)

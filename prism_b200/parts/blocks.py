@@ -5,13 +5,15 @@ that follows it (the next block's first norm, or the final norm).
 ``parallel``: one norm whose output both the mixer and the feed-forward read;
 their two results are added to the residual stream together.
 ``postnorm``: the residual stream itself is normed after every sum,
-``x <- norm(alpha x + sublayer(x))``, and the sublayers read x as it is."""
+``x <- norm(alpha x + sublayer(x))``, and the sublayers read x as it is.
+``hyper``: pre-norm sublayers around a residual stream kept in several
+copies, with learned weights for reading it and for writing back."""
 
 from __future__ import annotations
 
 from typing import Optional
 
-from .base import Block, ParamSpec, PartSpec, build_part, register_part
+from .base import Block, ParamSpec, PartSpec, StreamUpdate, WeightSource, build_part, register_part
 from .. import ops
 
 
@@ -136,3 +138,63 @@ class PostNormBlock(Block):
         # the next block of this kind starts from these rows: no second rounding pass over x
         ctx.scratch["postnorm_rows"], ctx.scratch["postnorm_rows_of"] = h, x
         return x, None
+
+
+@register_part("block", "hyper")
+class HyperBlock(Block):
+    """Hyper-connections: the residual stream is ``streams`` copies ``x_1 .. x_s`` (all equal to the embedding's
+    rows at the start).  Around sublayer q (1: the mixer, 2: the feed-forward) with its weights ``in_q [s]``,
+    ``mix_q [s, s]`` (indexed from, to) and ``out_q [s]``::
+
+        u = sum_i in_q[i] x_i;    y = sublayer(norm_q(u));    x_j <- sum_i mix_q[i, j] x_i + out_q[j] y
+
+    for all j at once from the old copies.  After the last layer the stream is the sum of the copies (the model's
+    final norm reads that).  Each update is left open (a ``StreamUpdate``) and carried out by the launch that
+    forms the next read-in and its norm, so the copies are read and written once per sublayer, in float32.
+    ``feed_forward`` None: the layer has a mixer only.  ``learned`` False: no connection weights at all (reading
+    sums the copies, writing adds the result to each; with one copy this is the plain pre-norm residual layer).
+    ``names``: the tensors of a sublayer's connection, after
+    ``hc1.`` / ``hc2.`` (keys in, mix, out)."""
+
+    NAMES = dict(inp="in", mix="mix", out="out")
+
+    def __init__(self, streams: int, mixer: PartSpec, mixer_norm: PartSpec, feed_forward: Optional[PartSpec] = None,
+                 ff_norm: Optional[PartSpec] = None, names: Optional[dict] = None, prefixes=("hc1.", "hc2."),
+                 learned: bool = True):
+        self.streams, self.learned = int(streams), bool(learned)
+        if not 1 <= self.streams <= 8:
+            raise ValueError(f"hyper-connections with {self.streams} streams: the kernel keeps 1 to 8 copies")
+        self.mixer_norm = self.add_child("mixer_norm", build_part("norm", mixer_norm))
+        self.mixer = self.add_child("mixer", build_part("mixer", mixer))
+        self.feed_forward = (self.add_child("feed_forward", build_part("feed_forward", feed_forward))
+                             if feed_forward is not None else None)
+        self.ff_norm = self.add_child("ff_norm", build_part("norm", ff_norm)) if feed_forward is not None else None
+        if self.feed_forward is not None and ff_norm is None:
+            raise ValueError("a hyper block with a feed-forward needs its norm")
+        self.names, self.prefixes = dict(self.NAMES, **(names or {})), tuple(prefixes)
+
+    def params(self):
+        s, n, ps = self.streams, self.names, []
+        if not self.learned:
+            return ps
+        for q, pre in enumerate(self.prefixes[:2 if self.feed_forward is not None else 1], start=1):
+            ps += [ParamSpec(f"in{q}", (WeightSource(pre + n["inp"], (s,), "norm"),)),
+                   ParamSpec(f"mix{q}", (WeightSource(pre + n["mix"], (s, s), "eye"),)),
+                   ParamSpec(f"out{q}", (WeightSource(pre + n["out"], (s,), "norm"),))]
+        return ps
+
+    def forward(self, ctx, residual, delta, cache):
+        s, x = self.streams, residual
+        if x.dim() == 2:                           # the first block of this kind: every copy starts as these rows
+            x_out = ctx.alloc((s,) + tuple(x.shape), x.dtype)
+        else:
+            if x.shape[0] != s:
+                raise ValueError(f"this block keeps {s} copies of the residual stream, the one before it {x.shape[0]}")
+            x_out = x
+        w = self.w.get
+        h = self.mixer_norm.forward_streams(ctx, x, s, x_out, delta, w("in1"))
+        d = StreamUpdate(self.mixer.forward(ctx, h, cache), w("mix1"), w("out1"))
+        if self.feed_forward is not None:
+            h = self.ff_norm.forward_streams(ctx, x_out, s, x_out, d, w("in2"))
+            d = StreamUpdate(self.feed_forward.forward(ctx, h), w("mix2"), w("out2"))
+        return x_out, d

@@ -1,7 +1,8 @@
 """Feed-forward parts.  ``swiglu``: andre-fu/prism's dense MLP
 (engine/executor.py:125-127): fused gate/up projection, ``silu(gate) * up``,
 down projection; no biases (engine/weight_pool.py:194-199).  ``mlp``: up
-projection, an elementwise activation, down projection."""
+projection, an elementwise activation, down projection.  ``moe``: a router
+sends every token through a few of many small gated layers."""
 
 from __future__ import annotations
 
@@ -69,3 +70,41 @@ class ActMLP(FeedForward):
 
     def forward(self, ctx, x):
         return ops.feed_forward_act(ctx, x, self.w["up_w"], self.w["down_w"], self.activation)
+
+
+@register_part("feed_forward", "moe")
+class MixtureOfExperts(FeedForward):
+    """``experts`` gated layers ``down_e(act(gate_e(a)) * up_e(a))`` without biases, of which each token uses ``top``:
+    router logits ``z = W_router h`` in float32, scores ``sigmoid(z)`` (``softmax`` True: their softmax), the ``top``
+    largest chosen; a choice's weight is its score (``renorm``: divided by the sum of the chosen) and multiplies the
+    expert's input, ``out = sum_e expert_e(w_e h)`` (``scale_input`` False: its output).  The result is a float32
+    stack with one plane per choice, which the next norm adds to the residual stream.  ``names``: the router's
+    tensor, the prefix pattern of an expert (``{e}``: its index), and its gate, up and down tensors."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, experts: int, top: int, softmax: bool = False,
+                 renorm: bool = False, scale_input: bool = True, activation: str = "silu",
+                 names=("router", "e{e}.", "gate", "up", "down")):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.experts, self.top = int(experts), int(top)
+        if not 1 <= self.top <= self.experts:
+            raise ValueError(f"a token uses {self.top} of {self.experts} experts: between 1 and all of them")
+        if activation not in ops.MOE_ACTS:
+            raise ValueError(f"activation {activation!r}: one of {sorted(ops.MOE_ACTS)}")
+        self.softmax, self.renorm, self.scale_input, self.activation = bool(softmax), bool(renorm), bool(scale_input), activation
+        self.names = tuple(names)
+
+    def params(self):
+        H, I, (router, pat, gate, up, down) = self.hidden_size, self.intermediate_size, self.names
+        gu, dn = [], []
+        for e in range(self.experts):
+            p = pat.format(e=e)
+            gu += [WeightSource(p + gate, (I, H)), WeightSource(p + up, (I, H))]
+            dn.append(WeightSource(p + down, (H, I)))
+        return [ParamSpec("router_w", (WeightSource(router, (self.experts, H)),)),
+                ParamSpec("gate_up_w", tuple(gu)), ParamSpec("down_w", tuple(dn))]
+
+    def forward(self, ctx, x):
+        H, I, E = self.hidden_size, self.intermediate_size, self.experts
+        logits = ops.linear(x, self.w["router_w"], None, out_dtype=ops.torch.float32)
+        return ops.moe_feed_forward(ctx, x, logits, self.w["gate_up_w"].view(E, 2 * I, H), self.w["down_w"].view(E, H, I),
+                                    self.top, self.softmax, self.renorm, self.scale_input, self.activation)

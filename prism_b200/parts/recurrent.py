@@ -9,6 +9,10 @@ the output projection is rounded to the compute dtype once.
 short causal convolution over time of q, k and v.
 ``wkv``: token-shift mixes of the input, a per-channel decay from a low-rank
 product, and a bonus for the current token in the read-out.
+``channel_delta``: the delta rule with one decay per key channel, from a
+low-rank product, and a low-rank sigmoid gate on the read-out.
+``rglru``: a recurrence with one number of state per channel whose gates are
+block-diagonal products, behind a short convolution, beside a gelu branch.
 ``sum``: several mixers side by side on the same input, their results scaled
 and added (one joint input product and one joint output product where the
 mixers can hand theirs over).
@@ -116,6 +120,156 @@ class GatedDeltaMixer(Mixer):
     def forward(self, ctx, x, cache):
         inner = ctx.alloc((x.shape[0], self.H * self.dv), ctx.dtype)
         self.forward_inner(ctx, x, cache, inner)
+        return ops.linear_delta(inner, self.w["o_w"], None, f32=True)
+
+
+@register_part("mixer", "channel_delta")
+class ChannelDeltaMixer(Mixer):
+    """The gated delta rule with a decay of its own for every key channel.  With h the input, per token (``G =
+    num_kv_heads`` q/k heads of ``head_dim``, ``H = num_heads`` value heads of ``v_head_dim``; head i uses q/k head
+    ``i // (H / G)``)::
+
+        q, k, v = silu(conv(W_q h)), silu(conv(W_k h)), silu(conv(W_v h))     conv: causal over time, per channel
+        q <- q / sqrt(sum q^2 + unit_eps) / sqrt(head_dim);   k <- k / sqrt(sum k^2 + unit_eps)      per head
+        beta = sigmoid(W_b h)                                                                        per head
+        w = exp(-exp(A_log) softplus(W_a2 (W_a1 h) + dt_bias))            per head and key channel, A_log per head
+        S <- diag(w) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q                           per head
+        out = W_o [o / rms(o) * norm * sigmoid(W_g2 (W_g1 h))]
+
+    State per request: S ``[H, v_head_dim, head_dim]`` (stored column by column) and the convolution's last
+    ``conv - 1`` inputs, both float32, both starting at zero.  The second halves of the two low-rank products run in
+    float32 with their epilogues (softplus and exponential; sigmoid) in the same launch.  ``names``: keys q, k, v,
+    q_conv, k_conv, v_conv, b, a1, a2, A_log, dt_bias, g1, g2, norm, o."""
+
+    NAMES = dict(q="q", k="k", v="v", q_conv="q.conv", k_conv="k.conv", v_conv="v.conv", b="b", a1="a1", a2="a2",
+                 A_log="A_log", dt_bias="dt_bias", g1="g1", g2="g2", norm="norm", o="o")
+    graph_safe = True
+    float32_projection = True
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int, conv: int,
+                 decay_rank: int, gate_rank: int, eps: float, unit_eps: float = 1e-6, out_scale: float = 1.0,
+                 names: Optional[dict] = None):
+        self.hidden_size, self.H, self.G = int(hidden_size), int(num_heads), int(num_kv_heads)
+        self.dk, self.dv, self.K = int(head_dim), int(v_head_dim), int(conv)
+        self.Ra, self.Rg = int(decay_rank), int(gate_rank)
+        if min(self.H, self.G, self.dk, self.dv, self.K, self.Ra, self.Rg) < 1 or self.H % self.G:
+            raise ConfigError(f"channel delta mixer: heads {self.H} must be a multiple of kv_heads {self.G}, and heads, "
+                              f"sizes, ranks and the convolution's taps positive")
+        if self.dk > 1024:
+            raise ConfigError(f"channel delta mixer: head_dim {self.dk} exceeds the scan kernel's 1024")
+        self.eps, self.unit_eps, self.out_scale = float(eps), float(unit_eps), float(out_scale)
+        self.names = dict(self.NAMES, **(names or {}))
+        self.C = 2 * self.G * self.dk + self.H * self.dv          # channels of the convolution: q | k | v
+        self.b_off, self.a_off, self.g_off = self.C, self.C + self.H, self.C + self.H + self.Ra
+        self.in_width = self.C + self.H + self.Ra + self.Rg       # q | k | v | b | a1 | g1
+
+    def cache_needs(self):
+        return (CacheNeed("state", state_shape=(self.H, self.dv, self.dk)),
+                CacheNeed("state", state_shape=(self.K - 1, self.C)))
+
+    def params(self):
+        W, n, G, H, dk, dv, K = self.hidden_size, self.names, self.G, self.H, self.dk, self.dv, self.K
+        return [ParamSpec("in_w", (WeightSource(n["q"], (G * dk, W)), WeightSource(n["k"], (G * dk, W)),
+                                   WeightSource(n["v"], (H * dv, W)), WeightSource(n["b"], (H, W)),
+                                   WeightSource(n["a1"], (self.Ra, W)), WeightSource(n["g1"], (self.Rg, W)))),
+                ParamSpec("taps", (WeightSource(n["q_conv"], (G * dk, K)), WeightSource(n["k_conv"], (G * dk, K)),
+                                   WeightSource(n["v_conv"], (H * dv, K)))),
+                ParamSpec("a2", (WeightSource(n["a2"], (H * dk, self.Ra)),)),
+                ParamSpec("g2", (WeightSource(n["g2"], (H * dv, self.Rg)),)),
+                ParamSpec("A_log", (WeightSource(n["A_log"], (H,), "bias"),)),
+                ParamSpec("dt_bias", (WeightSource(n["dt_bias"], (H * dk,), "bias"),)),
+                ParamSpec("norm", (WeightSource(n["norm"], (dv,), "norm"),)),
+                ParamSpec("o_w", (WeightSource(n["o"], (W, H * dv)),))]
+
+    def on_bound(self):
+        # the second halves run in float32 whatever the engine's dtype; transposed, so that the kernel's neighbouring
+        # threads read neighbouring floats
+        self.a2t = self.w["a2"].float().t().contiguous() if self.w["a2"] is not None else None
+        self.g2t = self.w["g2"].float().t().contiguous() if self.w["g2"] is not None else None
+
+    def forward(self, ctx, x, cache):
+        state, tail = cache
+        T, H, G, dk, dv = x.shape[0], self.H, self.G, self.dk, self.dv
+        proj = ops.linear(x, self.w["in_w"], None, out_dtype=torch.float32)
+        qkv = ctx.alloc((T, self.C), torch.float32)
+        beta = ctx.alloc((T, H), torch.float32)
+        single = ctx.decode_only          # one token per request: the kernel that reads the tail also moves it up
+        ops.conv_unit_gates(proj, self.b_off, 0, self.w["taps"], tail.state, None, None, ctx, G, H, dk, dv, self.unit_eps,
+                            qkv, beta, move_tail=single)
+        if not single:
+            ops.state_tail(proj, tail.state, ctx)
+        ww = ctx.alloc((T, H * dk), torch.float32)
+        ops.lowrank_decay(proj[:, self.a_off:self.a_off + self.Ra], self.a2t, self.w["dt_bias"], ww, inner_tanh=False,
+                          epilogue=ops.LR_SOFTPLUS, rate_log=self.w["A_log"], per=dk)
+        gate = ctx.alloc((T, H * dv), torch.float32)
+        ops.lowrank_decay(proj[:, self.g_off:self.g_off + self.Rg], self.g2t, None, gate, inner_tanh=False,
+                          epilogue=ops.LR_SIGMOID)
+        o = ctx.alloc((T, H, dv), torch.float32)
+        ops.recurrent_scan(ops.SCAN_CHANNEL, qkv[:, :G * dk], qkv[:, G * dk:2 * G * dk], qkv[:, 2 * G * dk:], state.state, ctx,
+                           H, H // G, dk, dv, o, bg=beta, ww=ww)
+        inner = ctx.alloc((T, H * dv), ctx.dtype)
+        ops.headnorm_gate(o, gate, self.w["norm"], self.eps, self.out_scale, inner, gate_act="none")
+        return ops.linear_delta(inner, self.w["o_w"], None, f32=True)
+
+
+@register_part("mixer", "rglru")
+class RGLRUMixer(Mixer):
+    """A recurrent block around a real-gated linear recurrent unit.  With h the input and two branches of
+    ``width`` channels::
+
+        y = gelu_tanh(W_y h + b_y);    u = conv(W_x h + b_x) + b_conv          conv: causal over time, per channel
+        r = sigmoid(Wr[b] u_b + br[b]);  i = sigmoid(Wi[b] u_b + bi[b])         per block b of width / blocks channels
+        a = exp(-decay_scale r softplus(lam));   S <- a S + sqrt(1 - a^2) i u   per channel, S = 0 before the first token
+        out = W_o (S y)
+
+    State per request: S ``[width]`` and the convolution's last ``conv - 1`` inputs, float32, starting at zero.
+    Both branches come from one product with float32 results; the gates, the coefficients and the recurrence are
+    float32 (``csrc/rglru.cu``).  ``names``: keys y, y_b, x, x_b, conv, conv_b, ra, ra_b, ri, ri_b, lam, o."""
+
+    NAMES = dict(y="y", y_b="y.b", x="x", x_b="x.b", conv="conv", conv_b="conv.b", ra="ra", ra_b="ra.b", ri="ri",
+                 ri_b="ri.b", lam="lam", o="o")
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, width: int, blocks: int, conv: int, decay_scale: float = 8.0,
+                 names: Optional[dict] = None):
+        self.hidden_size, self.C, self.blocks, self.K = int(hidden_size), int(width), int(blocks), int(conv)
+        if min(self.C, self.blocks, self.K) < 1 or self.C % self.blocks:
+            raise ConfigError(f"rglru mixer: width {self.C} must be a multiple of blocks {self.blocks}, and the "
+                              f"convolution's taps positive")
+        self.bs, self.decay_scale = self.C // self.blocks, float(decay_scale)
+        self.names = dict(self.NAMES, **(names or {}))
+
+    def cache_needs(self):
+        return (CacheNeed("state", state_shape=(self.C,)), CacheNeed("state", state_shape=(self.K - 1, self.C)))
+
+    def params(self):
+        W, C, n, nb, bs = self.hidden_size, self.C, self.names, self.blocks, self.bs
+        return [ParamSpec("in_w", (WeightSource(n["y"], (C, W)), WeightSource(n["x"], (C, W)))),
+                ParamSpec("in_b", (WeightSource(n["y_b"], (C,), "bias"), WeightSource(n["x_b"], (C,), "bias"))),
+                ParamSpec("taps", (WeightSource(n["conv"], (C, self.K)),)),
+                ParamSpec("conv_b", (WeightSource(n["conv_b"], (C,), "bias"),)),
+                ParamSpec("ra", (WeightSource(n["ra"], (nb, bs, bs)),)),
+                ParamSpec("ri", (WeightSource(n["ri"], (nb, bs, bs)),)),
+                ParamSpec("ra_b", (WeightSource(n["ra_b"], (nb, bs), "bias"),)),
+                ParamSpec("ri_b", (WeightSource(n["ri_b"], (nb, bs), "bias"),)),
+                ParamSpec("lam", (WeightSource(n["lam"], (C,), "bias"),)),
+                ParamSpec("o_w", (WeightSource(n["o"], (W, C)),))]
+
+    def forward(self, ctx, x, cache):
+        state, tail = cache
+        T, C = x.shape[0], self.C
+        proj = ops.linear(x, self.w["in_w"], self.w["in_b"], out_dtype=torch.float32)      # y | x
+        xb = proj[:, C:]
+        u = ctx.alloc((T, C), torch.float32)
+        single = ctx.decode_only
+        ops.causal_conv(xb, self.w["taps"], self.w["conv_b"], tail.state, ctx, u, move_tail=single)
+        if not single:
+            ops.state_tail(xb, tail.state, ctx)
+        ag = ctx.alloc((2, T, C), torch.float32)
+        ops.block_gates(u, self.w["ra"], self.w["ri"], self.w["ra_b"], self.w["ri_b"], self.w["lam"], self.decay_scale,
+                        ag[0], ag[1])
+        inner = ctx.alloc((T, C), ctx.dtype)
+        ops.rglru_scan(ag[0], ag[1], proj[:, :C], state.state, ctx, inner, gelu=True)
         return ops.linear_delta(inner, self.w["o_w"], None, f32=True)
 
 

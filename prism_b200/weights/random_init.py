@@ -39,6 +39,8 @@ def file_tensors(model) -> Iterator[Tuple[str, tuple, str]]:
 
 def _draw(shape, init: str, gen: torch.Generator, device="cpu") -> torch.Tensor:
     t = torch.randn(shape, generator=gen, dtype=torch.float32, device=device) * STD
+    if init == "eye":                # a square matrix near the identity (weights that mix copies of a stream)
+        return t + torch.eye(shape[0], dtype=torch.float32, device=device)
     return t + 1.0 if init == "norm" else t
 
 
@@ -60,6 +62,8 @@ def write_model_folder(raw_config: dict, seed: int, out_dir: str,
         for idx, (name, shape, init) in enumerate(file_tensors(model)):
             gen = torch.Generator(device=device).manual_seed(int(seed) + idx)
             t = torch.empty(shape, dtype=store_dtype, device=device).normal_(0.0, STD, generator=gen)
+            if init == "eye":
+                t.add_(torch.eye(shape[0], dtype=store_dtype, device=device))
             tensors[name] = (t.add_(1.0) if init == "norm" else t).cpu()
     os.makedirs(out_dir, exist_ok=True)
     raw["torch_dtype"] = {torch.bfloat16: "bfloat16", torch.float32: "float32"}.get(store_dtype, str(store_dtype))
@@ -87,6 +91,8 @@ def random_pool(model, seed: int, device, compute_dtype: torch.dtype) -> StaticW
                 view.copy_(torch.empty(view.shape, dtype=view.dtype, device=view.device).normal_(0.0, STD, generator=gen))
             if s.init == "norm":
                 view.add_(1.0)
+            elif s.init == "eye":
+                view.add_(torch.eye(view.shape[0], dtype=view.dtype, device=view.device))
             idx += 1
     model.bind(pool.tensors, torch.device(device), compute_dtype)
     return pool
