@@ -197,7 +197,10 @@ def moe(h, w, p, mlp):
 # ---- the model ----------------------------------------------------------------
 
 def hyper_step(xs, hc, w, sublayer):
-    """One sublayer under hyper-connections: ``xs [s, T, D]`` -> new streams."""
+    """One sublayer under hyper-connections: ``xs [s, T, D]`` -> new streams.  A model without connection weights
+    keeps one stream: ``x <- x + sublayer(x)``."""
+    if hc + "in" not in w:
+        return xs + sublayer(xs[0])[None]
     u = torch.einsum("s,std->td", w[hc + "in"], xs)
     y = sublayer(u)
     return torch.einsum("sr,std->rtd", w[hc + "mix"], xs) + w[hc + "out"][:, None, None] * y[None]
@@ -207,7 +210,7 @@ def forward(cfg, w, tokens, return_layers=False):
     """Logits ``[T, vocab]`` of one sequence; with ``return_layers`` also the sum of the streams after every layer."""
     eps = cfg["norm"]["eps"]
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
-    xs = x[None].repeat(cfg["streams"], 1, 1)
+    xs = x[None].repeat(cfg.get("streams") or 1, 1, 1)
     kvs, after = {}, []
     for i, layer in enumerate(cfg["layers"]):
         p, m = f"l{i}.", layer["mixer"]
