@@ -1,8 +1,8 @@
-"""Prefill and decode throughput of the Dolezen or the Pofazen design at layer sizes that resemble real models
+"""Prefill and decode throughput of the Dolezen, the Pofazen or the Zuvulorn design at layer sizes that resemble real models
 (random weights, bf16), beside the Qwen2 architecture at equal width, depth and parameter count, and the
 design's own kernels beside Qwen2's on the same problem with their fractions of the measured peaks.
 
-    python bench.py --design dolezen|pofazen [--sizes 2k,4k] [--steps K] [--warmup W]
+    python bench.py --design dolezen|pofazen|zuvulorn [--sizes 2k,4k] [--steps K] [--warmup W]
     python benchmarks/design_bench.py [--design pofazen] [--sizes 2k] [--kernels-only] [--once KERNEL]
 
 One JSON line.  Timing: CUDA events after W >= 3 warm-up runs; every timed step reads all weights (more than
@@ -67,6 +67,37 @@ def pofazen_config(s):
               for i in range(s["layers"])]
     return dict(architecture="Pofazen", vocab=s["vocab"], width=s["width"], norm=dict(eps=1e-6), postln_alpha=2.0,
                 layers=layers, max_positions=8192)
+
+
+MOE_EXPERTS, MOE_TOP = 8, 2
+
+
+def zuvulorn_config(s):
+    """Layers: attention with keys of its own, attention on the keys of the layer before, delta rule with a decay
+    per key channel, real-gated linear recurrence, ...; every layer under hyper-connections with two copies of the
+    stream and a mixture of 8 experts (2 per token) whose weights together are Qwen2's feed-forward."""
+    att = dict(heads=s["heads"], kv_heads=s["kv_heads"], dim=s["dim"], vdim=s["vdim"], scale=s["dim"] ** -0.5,
+               rot=dict(base=500000.0, dims=s["dim"], scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)))
+    cd = dict(heads=s["heads"], kv_heads=s["kv_heads"], dim=s["dim"], vdim=s["vdim"], conv=4, decay_rank=64, gate_rank=64)
+    rg = dict(width=s["width"], blocks=s["width"] // 128, conv=4)
+    mlp = dict(kind="moe", expert=dict(ff=moe_ff(s)), router=dict(experts=MOE_EXPERTS, top=MOE_TOP))
+    layers = []
+    for i in range(s["layers"]):
+        k = i % 4
+        if k == 0:
+            layers.append(dict(type="attention", mixer=dict(att), mlp=mlp))
+        elif k == 1:
+            layers.append(dict(type="attention", mixer=dict(att, kv_from=i - 1), mlp=mlp))
+        elif k == 2:
+            layers.append(dict(type="channel_delta", mixer=cd, mlp=mlp))
+        else:
+            layers.append(dict(type="rglru", mixer=rg, mlp=mlp))
+    return dict(architecture="Zuvulorn", vocab=s["vocab"], width=s["width"], norm=dict(eps=1e-6), streams=2, layers=layers,
+                max_positions=8192)
+
+
+def moe_ff(s):
+    return s["ff"] * 2 // 3 // 256 * 256 // MOE_EXPERTS // 32 * 32
 
 
 def qwen2_config(s):
@@ -331,7 +362,120 @@ def pofazen_kernel_numbers(s, pk, once=None):
     return out
 
 
-DESIGNS = {"dolezen": (dolezen_config, kernel_numbers), "pofazen": (pofazen_config, pofazen_kernel_numbers)}
+def zuvulorn_kernel_numbers(s, pk, once=None):
+    """The design's kernels alone, each beside the like kernel of the closest model on the same problem: causal
+    attention with one added to the denominator beside Qwen2's causal kernels; the delta rule with a decay per
+    key channel beside the delta rule with one decay per head; the real-gated recurrence with its gates; the
+    experts' grouped products beside Qwen2's dense feed-forward of the same total weight; the norm that also
+    updates and reads the copies of the stream beside the plain add + norm."""
+    from prism_b200 import ops
+    out = {}
+    T = 2048
+    nh, nkv, dk, dv, W = s["heads"], s["kv_heads"], s["dim"], s["vdim"], s["width"]
+    shapes = (("prefill_2048", 1, 0, T), ("decode_b8", 8, T - 1, 1), ("decode_b64", 64, T - 1, 1))
+    causal = ops.KeyMask.causal()
+
+    def run(name, fn, flops, nbytes, fp32=False):
+        if once:
+            if once == name:
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize()
+            return
+        ms = timeit(fn)
+        if fp32:
+            out[name] = dict(us=round(ms * 1e3, 1), fp32_tflops=round(flops / ms / 1e9, 2), gbs=round(nbytes / ms / 1e6, 1),
+                             frac_hbm_of_measured=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4))
+        else:
+            out[name] = _rates(ms, flops, nbytes, pk)
+
+    sink = torch.zeros(nh, device=DEV)
+    for label, batch, cached, q_len in shapes:
+        c, kc, vc, bt, npages = paged(batch, cached, q_len, nkv, dk, dv)
+        q = torch.randn(batch * q_len, nh, dk, device=DEV, dtype=torch.bfloat16)
+        o = torch.empty(batch * q_len, nh * dv, device=DEV, dtype=torch.bfloat16)
+        pairs = batch * visible_pairs(cached, q_len, causal)
+        flops = 2 * pairs * nh * (dk + dv)
+        nbytes = 2 * (batch * (cached + q_len) * nkv * (dk + dv) + batch * q_len * nh * (dk + dv))
+        run(f"sink_causal_{label}", lambda: ops.masked_attention(c, q, o, kc, vc, bt, npages, causal, dk ** -0.5, sink), flops, nbytes)
+        if q_len == 1:
+            ns = ops.decode_splits(batch, nkv, cached + 1, None)
+            po = torch.empty(batch, nh, ns, dk, device=DEV)
+            pml = torch.empty(batch, nh, ns, 2, device=DEV)
+            run(f"qwen2_causal_{label}", lambda: ops.attention_decode_bf16(q, o, kc, vc, bt, c.positions, c.tok_seg, npages, None,
+                                                                           dk ** -0.5, ns, po, pml, c.err), flops, nbytes)
+        else:
+            run(f"qwen2_causal_tcgen05_{label}", lambda: ops.attention_prefill_tc(q, o, kc, vc, bt, c.seg_start, c.cached_len, q_len,
+                                                                                  npages, None, dk ** -0.5, c.err), flops, nbytes)
+            run(f"qwen2_causal_mma_sync_{label}", lambda: ops.attention_prefill_bf16(q, o, kc, vc, bt, c.seg_start, c.cached_len,
+                                                                                     q_len, npages, None, dk ** -0.5, c.err), flops, nbytes)
+    # the matrix-state scans: a decay per key channel (this design) beside one per head (the like kernel)
+    H, rep, G = nh, nh // nkv, nkv
+    for label, batch, cached, q_len in shapes:
+        Tt = batch * q_len
+        c = types.SimpleNamespace(seg_start=(torch.arange(batch + 1, dtype=torch.int32) * q_len).to(DEV),
+                                  state_slots=torch.arange(batch, dtype=torch.int32, device=DEV), S=batch, max_q_len=q_len)
+        state = torch.zeros(batch + 1, H, dv, dk, device=DEV)
+        o = torch.empty(Tt, H, dv, device=DEV)
+        x = torch.nn.functional.normalize(torch.randn(Tt, 2 * G + H, dk, device=DEV), dim=-1).view(Tt, -1)
+        beta = torch.rand(Tt, H, device=DEV)
+        bg = torch.rand(Tt, 2 * H, device=DEV) * 0.5 + 0.5
+        ww = torch.rand(Tt, H * dk, device=DEV) * 0.5 + 0.5
+        flops = 6 * Tt * H * dk * dv
+        nbytes = 4 * (2 * batch * H * dk * dv + Tt * H * (2 * dk + 2 * dv))
+        run(f"channel_scan_{label}", lambda: ops.recurrent_scan(ops.SCAN_CHANNEL, x[:, :G * dk], x[:, G * dk:2 * G * dk], x[:, 2 * G * dk:],
+                                                                state, c, H, rep, dk, dv, o, bg=beta, ww=ww), flops, nbytes, fp32=True)
+        run(f"delta_scan_{label}", lambda: ops.recurrent_scan(ops.SCAN_DELTA, x[:, :G * dk], x[:, G * dk:2 * G * dk], x[:, 2 * G * dk:],
+                                                              state, c, H, rep, dk, dv, o, bg=bg), flops, nbytes, fp32=True)
+    # the real-gated recurrence: gates (two block-diagonal products, float32) and the scan per channel
+    C, nb = W, W // 128
+    bs = C // nb
+    wr, wi = (torch.randn(nb, bs, bs, device=DEV, dtype=torch.bfloat16) / bs ** 0.5 for _ in range(2))
+    br, bi, lam = (torch.zeros(nb, bs, device=DEV, dtype=torch.bfloat16) for _ in range(2)) , None, torch.zeros(C, device=DEV, dtype=torch.bfloat16)
+    br, bi = br
+    for label, batch, cached, q_len in shapes:
+        Tt = batch * q_len
+        c = types.SimpleNamespace(seg_start=(torch.arange(batch + 1, dtype=torch.int32) * q_len).to(DEV),
+                                  state_slots=torch.arange(batch, dtype=torch.int32, device=DEV), S=batch)
+        u, y = torch.randn(Tt, C, device=DEV), torch.randn(Tt, C, device=DEV)
+        ag = torch.empty(2, Tt, C, device=DEV)
+        st = torch.zeros(batch + 1, C, device=DEV)
+        o = torch.empty(Tt, C, device=DEV, dtype=torch.bfloat16)
+        run(f"block_gates_{label}", lambda: ops.block_gates(u, wr, wi, br, bi, lam, 8.0, ag[0], ag[1]), 4 * Tt * C * bs,
+            4 * 3 * Tt * C + 2 * 2 * nb * bs * bs, fp32=True)
+        run(f"rglru_scan_{label}", lambda: ops.rglru_scan(ag[0], ag[1], y, st, c, o), 3 * Tt * C, 4 * 3 * Tt * C + 2 * Tt * C + 8 * batch * C,
+            fp32=True)
+    # the experts beside the dense feed-forward of the same total weight
+    E, top, F = MOE_EXPERTS, MOE_TOP, moe_ff(s)
+    Fd = s["ff"] * 2 // 3 // 256 * 256
+    gu = torch.randn(E, 2 * F, W, device=DEV, dtype=torch.bfloat16) / W ** 0.5
+    dn = torch.randn(E, W, F, device=DEV, dtype=torch.bfloat16) / F ** 0.5
+    gud = torch.randn(2 * Fd, W, device=DEV, dtype=torch.bfloat16) / W ** 0.5
+    dnd = torch.randn(W, Fd, device=DEV, dtype=torch.bfloat16) / Fd ** 0.5
+    actx = types.SimpleNamespace(alloc=lambda shape, dtype: torch.empty(shape, dtype=dtype, device=DEV))
+    for label, Tt in (("prefill_2048", T), ("decode_b8", 8), ("decode_b64", 64)):
+        xx = torch.randn(Tt, W, device=DEV, dtype=torch.bfloat16)
+        logits = torch.randn(Tt, E, device=DEV)
+        used = min(E, Tt * top)
+        run(f"experts_{label}", lambda: ops.moe_feed_forward(actx, xx, logits, gu, dn, top), 6 * Tt * top * F * W,
+            2 * (3 * used * F * W + Tt * W * (1 + 2 * top)))
+        run(f"qwen2_feed_forward_{label}", lambda: ops.feed_forward_swiglu(actx, xx, gud, dnd), 6 * Tt * Fd * W,
+            2 * (3 * Fd * W + 3 * Tt * W))
+    # the norm that carries out the stream update and the read-in, beside add + norm on one stream
+    wn = torch.ones(W, device=DEV)
+    for label, Tt in (("prefill_2048", T), ("decode_b64", 64)):
+        xs = torch.randn(2, Tt, W, device=DEV)
+        d = torch.randn(Tt, W, device=DEV)
+        mix, ow, iw = torch.eye(2, device=DEV), torch.ones(2, device=DEV), torch.ones(2, device=DEV)
+        h = torch.empty(Tt, W, device=DEV, dtype=torch.bfloat16)
+        run(f"hyper_norm_{label}", lambda: ops.hyper_norm(xs, 2, xs, d, mix, ow, iw, wn, 1e-6, h), 0, 4 * Tt * W * 5 + 2 * Tt * W, fp32=True)
+        x1 = torch.randn(Tt, W, device=DEV)
+        run(f"qwen2_add_norm_{label}", lambda: ops.add_rmsnorm(x1, d, wn, 1e-6, h), 0, 4 * Tt * W * 3 + 2 * Tt * W, fp32=True)
+    return out
+
+
+DESIGNS = {"dolezen": (dolezen_config, kernel_numbers), "pofazen": (pofazen_config, pofazen_kernel_numbers),
+           "zuvulorn": (zuvulorn_config, zuvulorn_kernel_numbers)}
 
 
 def run(sizes, steps, warmup, prompt_len=2048, batch=8, kernels_only=False, once=None, peaks=None, design="dolezen"):

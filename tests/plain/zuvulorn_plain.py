@@ -2,7 +2,9 @@
 mechanism, for whole sequences on the CPU.  It shares no code with
 ``prism_b200``: weights come in as a dict of tensors keyed by the model file's
 tensor names, the configuration as the raw ``config.json`` dict.  Everything
-runs in the dtype of the weights handed in (float32 or float64).
+runs in the dtype of the weights handed in (float32 or float64).  ``rnd``, where a function takes it, is applied to
+what a 16-bit engine may keep in 16 bits (a sublayer's input, cached keys and values, rotated queries, what enters an
+output projection or an expert's second product); the default leaves everything as it is.
 
 Notation: ``x [T, D]`` is one sequence, positions are ``0 .. T-1``; ``W`` are
 stored ``[out, in]`` and applied as ``x @ W.T``.
@@ -93,7 +95,11 @@ def rotate_halves(x, positions, freqs):
 
 # ---- mixers -------------------------------------------------------------------
 
-def attention_keys(h, w, p, m, eps):
+def same(x):
+    return x
+
+
+def attention_keys(h, w, p, m, eps, rnd=same):
     """Keys (normed over the whole projection, rotated) ``[T, G, dim]`` and values ``[T, G, vdim]`` of a layer."""
     T = h.shape[0]
     G, dim, vdim = m["kv_heads"], m["dim"], m.get("vdim", m["dim"])
@@ -102,7 +108,7 @@ def attention_keys(h, w, p, m, eps):
     rot = m.get("rot") or {}
     freqs = band_frequencies(rot.get("base", 10000.0), rot.get("dims", 0), rot.get("scaling"), h.dtype)
     pos = torch.arange(T)
-    return rotate_halves(k.view(T, G, dim), pos, freqs), v.view(T, G, vdim)
+    return rnd(rotate_halves(k.view(T, G, dim), pos, freqs)), rnd(v.view(T, G, vdim))
 
 
 def sink_softmax(scores):
@@ -112,7 +118,7 @@ def sink_softmax(scores):
     return e / (torch.exp(-mx) + e.sum(-1, keepdim=True))
 
 
-def attention(h, w, p, m, eps, kv=None):
+def attention(h, w, p, m, eps, kv=None, rnd=same):
     """Grouped-query causal attention with a sink of score 0, a per-head sigmoid gate; ``kv``: another layer's
     keys and values (this layer then has no key/value tensors)."""
     T = h.shape[0]
@@ -120,8 +126,8 @@ def attention(h, w, p, m, eps, kv=None):
     q = rms(h @ w[p + "q"].T, eps) * w[p + "q.norm"]
     rot = m.get("rot") or {}
     freqs = band_frequencies(rot.get("base", 10000.0), rot.get("dims", 0), rot.get("scaling"), h.dtype)
-    q = rotate_halves(q.view(T, H, dim), torch.arange(T), freqs)
-    k, v = kv if kv is not None else attention_keys(h, w, p, m, eps)
+    q = rnd(rotate_halves(q.view(T, H, dim), torch.arange(T), freqs))
+    k, v = kv if kv is not None else attention_keys(h, w, p, m, eps, rnd)
     gate = torch.sigmoid(h @ w[p + "g"].T)                      # [T, H]
     causal = torch.ones(T, T, dtype=torch.bool).tril()
     out = torch.zeros(T, H, vdim, dtype=h.dtype)
@@ -130,10 +136,10 @@ def attention(h, w, p, m, eps, kv=None):
         s = (q[:, hh] @ k[:, g].T) * m["scale"]
         s = s.masked_fill(~causal, float("-inf"))
         out[:, hh] = (sink_softmax(s) @ v[:, g]) * gate[:, hh:hh + 1]
-    return out.reshape(T, H * vdim) @ w[p + "o"].T, (k, v)
+    return rnd(out.reshape(T, H * vdim)) @ w[p + "o"].T, (k, v)
 
 
-def rglru(h, w, p, m):
+def rglru(h, w, p, m, rnd=same):
     """Recurrent block with a real-gated linear recurrent unit."""
     T = h.shape[0]
     width, blocks = m["width"], m["blocks"]
@@ -150,10 +156,10 @@ def rglru(h, w, p, m):
     for t in range(T):
         S = a[t] * S + b[t]
         out[t] = S
-    return (out * y) @ w[p + "o"].T
+    return rnd(out * y) @ w[p + "o"].T
 
 
-def channel_delta(h, w, p, m, eps):
+def channel_delta(h, w, p, m, eps, rnd=same):
     """Gated delta rule with one decay per head and key channel."""
     T = h.shape[0]
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
@@ -176,12 +182,12 @@ def channel_delta(h, w, p, m, eps):
             S = S + torch.outer(k[t, kv], uu)
             out[t, hh] = S.T @ q[t, kv]
     out = rms(out, eps) * w[p + "norm"] * gate
-    return out.reshape(T, H * dv) @ w[p + "o"].T
+    return rnd(out.reshape(T, H * dv)) @ w[p + "o"].T
 
 
 # ---- feed-forward -------------------------------------------------------------
 
-def moe(h, w, p, mlp):
+def moe(h, w, p, mlp, rnd=same):
     """Sigmoid-scored top-k experts; the score multiplies the chosen expert's input."""
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
     s = torch.sigmoid(h @ w[p + "router"].T)
@@ -189,8 +195,8 @@ def moe(h, w, p, mlp):
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e in chosen[t].tolist():
-            x = s[t, e] * h[t]
-            out[t] += (silu(x @ w[f"{p}e{e}.gate"].T) * (x @ w[f"{p}e{e}.up"].T)) @ w[f"{p}e{e}.down"].T
+            x = rnd(s[t, e] * h[t])
+            out[t] += rnd(silu(x @ w[f"{p}e{e}.gate"].T) * (x @ w[f"{p}e{e}.up"].T)) @ w[f"{p}e{e}.down"].T
     return out
 
 
@@ -206,7 +212,7 @@ def hyper_step(xs, hc, w, sublayer):
     return torch.einsum("sr,std->rtd", w[hc + "mix"], xs) + w[hc + "out"][:, None, None] * y[None]
 
 
-def forward(cfg, w, tokens, return_layers=False):
+def forward(cfg, w, tokens, return_layers=False, rnd=same):
     """Logits ``[T, vocab]`` of one sequence; with ``return_layers`` also the sum of the streams after every layer."""
     eps = cfg["norm"]["eps"]
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
@@ -216,21 +222,21 @@ def forward(cfg, w, tokens, return_layers=False):
         p, m = f"l{i}.", layer["mixer"]
 
         def mixer(u):
-            hn = layer_norm(u, w[p + "norm1"], eps)
+            hn = rnd(layer_norm(u, w[p + "norm1"], eps))
             if layer["type"] == "attention":
                 src = m.get("kv_from")
-                y, kv = attention(hn, w, p + "mix.", m, eps, None if src is None else kvs[src])
+                y, kv = attention(hn, w, p + "mix.", m, eps, None if src is None else kvs[src], rnd)
                 kvs[i] = kv
                 return y
             if layer["type"] == "rglru":
-                return rglru(hn, w, p + "mix.", m)
+                return rglru(hn, w, p + "mix.", m, rnd)
             if layer["type"] == "channel_delta":
-                return channel_delta(hn, w, p + "mix.", m, eps)
+                return channel_delta(hn, w, p + "mix.", m, eps, rnd)
             raise ValueError(layer["type"])
 
         xs = hyper_step(xs, p + "hc1.", w, mixer)
         if layer.get("mlp") is not None:
-            xs = hyper_step(xs, p + "hc2.", w, lambda u: moe(layer_norm(u, w[p + "norm2"], eps), w, p + "mlp.", layer["mlp"]))
+            xs = hyper_step(xs, p + "hc2.", w, lambda u: moe(rnd(layer_norm(u, w[p + "norm2"], eps)), w, p + "mlp.", layer["mlp"], rnd))
         after.append(xs.sum(0))
-    logits = layer_norm(xs.sum(0), w["final.norm"], eps) @ w["head"].T
+    logits = rnd(layer_norm(xs.sum(0), w["final.norm"], eps)) @ w["head"].T
     return (logits, torch.stack(after)) if return_layers else logits
