@@ -3,7 +3,8 @@
 //   lower index wins a tie); the weight of a choice is its score, optionally divided by the sum of the chosen.
 // The (token, choice) pairs are sorted by expert on the device, so that each expert's rows are one stretch:
 //   prism_moe_route    top-k per token; counts[e] rows per expert, and each pair's rank among its expert's rows
-//   prism_moe_place    offs = prefix sums of counts; per sorted row: its token, its weight, and where its result goes
+//   prism_moe_place    offs = prefix sums of counts (each rounded up to `pad`); per sorted row: its token, its weight,
+//                      and where its result goes
 //   prism_moe_gemm     grouped product over the sorted rows, expert by expert, no host knowledge of the counts:
 //                      (dual)   hidden[p] = act(Wg[e] a_p) * (Wu[e] a_p),  a_p = x[token[p]] * (weight[p] or 1)
 //                      (single) y[dst[p]] = Wd[e] hidden[p] * (weight[p] or 1)
@@ -73,10 +74,11 @@ __global__ void moe_route_kernel(const float* __restrict__ logits_in, long long 
         for (int j = 0; j < top; ++j) sel_w[(size_t)t * top + j] /= chosen;
 }
 
-// offs [E + 1]; row_tok, row_w, row_dst [T top] in sorted order.
+// offs [E + 1]: every expert's stretch starts at a multiple of pad; row_tok, row_w, row_dst in sorted order (at the
+// padded places), or none of the three when row_tok is null.
 __global__ void moe_place_kernel(const int* __restrict__ counts_in, const int* __restrict__ sel_e_in,
                                  const float* __restrict__ sel_w_in, const int* __restrict__ sel_rank_in, int T, int E, int top,
-                                 int* __restrict__ offs, int* __restrict__ row_tok, float* __restrict__ row_w,
+                                 int pad, int* __restrict__ offs, int* __restrict__ row_tok, float* __restrict__ row_w,
                                  int* __restrict__ row_dst) {
     pdl_trigger();
     pdl_wait();
@@ -89,7 +91,7 @@ __global__ void moe_place_kernel(const int* __restrict__ counts_in, const int* _
         int acc = 0;
         for (int e = 0; e < E; ++e) {
             so[e] = acc;
-            acc += counts[e];
+            acc += (counts[e] + pad - 1) / pad * pad;
         }
         so[E] = acc;
     }
@@ -97,7 +99,7 @@ __global__ void moe_place_kernel(const int* __restrict__ counts_in, const int* _
     if (blockIdx.x == 0)
         for (int e = threadIdx.x; e <= E; e += blockDim.x) offs[e] = so[e];
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= T * top) return;
+    if (i >= T * top || row_tok == nullptr) return;
     const int t = i / top, j = i - t * top;
     const int p = so[sel_e[i]] + sel_rank[i];
     row_tok[p] = t;
@@ -239,12 +241,13 @@ PRISM_EXPORT int prism_moe_route(const float* logits, long long logits_stride, i
 }
 
 PRISM_EXPORT int prism_moe_place(const int* counts, const int* sel_e, const float* sel_w, const int* sel_rank, int T, int E,
-                                 int top, int* offs, int* row_tok, float* row_w, int* row_dst, cudaStream_t stream) {
+                                 int top, int pad, int* offs, int* row_tok, float* row_w, int* row_dst, cudaStream_t stream) {
     if (T <= 0) return 0;
+    if (pad < 1) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)(E + 1) * sizeof(int);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
     return (int)prism::launch_kernel(prism::moe_place_kernel, dim3((T * top + 255) / 256), dim3(256), smem, stream, counts, sel_e,
-                                     sel_w, sel_rank, T, E, top, offs, row_tok, row_w, row_dst);
+                                     sel_w, sel_rank, T, E, top, pad, offs, row_tok, row_w, row_dst);
 }
 
 // rows = T top sorted rows.  dual 1: a [T, K], w [E, 2 N, K], out [rows, N] of dtype; dual 0: a [rows, K], w [E, N, K],

@@ -107,7 +107,10 @@ class _Sig:
     prism_decay_from_exponent = [_p, _ll, _p, _i, _i, _i, _p]
     prism_lowrank_decay = [_p, _ll, _i, _p, _p, _i, _i, _i, _p, _ll, _i, _i, _p, _i, _i, _p]
     prism_moe_route = [_p, _ll, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p]
-    prism_moe_place = [_p, _p, _p, _p, _i, _i, _i, _p, _p, _p, _p, _p]
+    prism_moe_place = [_p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p]
+    prism_moe_tcgen05_supported = [_i, _i]
+    prism_moe_gather = [_p, _ll, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p, _p]
+    prism_moe_gemm_tcgen05 = [_p, _ll, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _ll, _p, _p]
     prism_moe_gemm = [_p, _ll, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _ll, _p]
     prism_hyper_norm = [_p, _ll, _p, _ll, _p, _i, _i, _ll, _p, _i, _p, _i, _p, _i, _i, _p, _i, _f, _i, _p, _i, _p, _i, _i, _p]
     prism_causal_conv = [_p, _ll, _p, _i, _p, _i, _i, _i, _p, _p, _p, _p, _i, _p, _ll, _i, _p]
@@ -1785,6 +1788,7 @@ def rglru_scan(a: torch.Tensor, g: torch.Tensor, y: torch.Tensor, state: torch.T
 
 
 MOE_ACTS = {"silu": 0, "gelu_tanh": 1, "relu": 2}      # csrc/moe.cu: moe_act
+moe_tensor_cores = True                                 # bf16 experts on tcgen05 (csrc/moe_tcgen05.cu); False: CUDA cores
 
 
 def moe_feed_forward(ctx, x: torch.Tensor, logits: torch.Tensor, gate_up_w: torch.Tensor, down_w: torch.Tensor, top: int,
@@ -1794,7 +1798,8 @@ def moe_feed_forward(ctx, x: torch.Tensor, logits: torch.Tensor, gate_up_w: torc
     ``top`` experts with the largest scores (sigmoid of the logits, or their softmax); a choice's weight is its score
     (``renorm``: over the sum of the chosen) and multiplies the expert's input (``scale_input``) or its output.
     Returns float32 ``[top, T, W]``: one plane per choice, which the next norm adds up.  The rows are sorted by
-    expert on the device and run as grouped products; the host never learns the counts."""
+    expert on the device and run as grouped products; the host never learns the counts.  bf16 with rows of 16-byte
+    multiples: tcgen05 tiles of one expert each (``csrc/moe_tcgen05.cu``); otherwise CUDA cores (``csrc/moe.cu``)."""
     _cuda(x, logits, gate_up_w, down_w)
     T, W = x.shape
     E, F2, _ = gate_up_w.shape
@@ -1804,6 +1809,36 @@ def moe_feed_forward(ctx, x: torch.Tensor, logits: torch.Tensor, gate_up_w: torc
     assert gate_up_w.dtype == x.dtype and down_w.dtype == x.dtype and 1 <= top <= E
     rows = T * top
     dev = x.device
+    L = lib()
+    si = 1 if scale_input else 0
+    if x.dtype == torch.bfloat16 and moe_tensor_cores and L.prism_moe_tcgen05_supported(W, F) and x.stride(0) % 8 == 0:
+        # tensor cores: every expert's rows start at a multiple of the token tile, one tile has one expert
+        ntok = 16 if T <= 16 else (32 if T <= 32 else 64)
+        tiles = min(rows, (rows + E * (ntok - 1)) // ntok)          # no more tiles than this, whatever the choice
+        padded = tiles * ntok
+        ints = torch.empty(E + (E + 1) + 2 * rows + padded, dtype=torch.int32, device=dev)
+        counts, offs = ints[:E], ints[E:2 * E + 1]
+        o = 2 * E + 1
+        sel_e, sel_rank, row_dst = ints[o:o + rows], ints[o + rows:o + 2 * rows], ints[o + 2 * rows:]
+        counts.zero_()
+        flt = torch.empty(rows + padded, dtype=torch.float32, device=dev)
+        sel_w, row_w = flt[:rows], flt[rows:]
+        err = _tc_err_word(dev)
+        _check(L.prism_moe_route(_ptr(logits), logits.stride(0), T, E, int(top), 1 if softmax else 0, 1 if renorm else 0,
+                                 _ptr(counts), _ptr(sel_e), _ptr(sel_w), _ptr(sel_rank), _stream()), "moe_route")
+        _check(L.prism_moe_place(_ptr(counts), _ptr(sel_e), _ptr(sel_w), _ptr(sel_rank), T, E, int(top), ntok, _ptr(offs), None,
+                                 None, None, _stream()), "moe_place")
+        xs = ctx.alloc((padded, W), x.dtype)
+        _check(L.prism_moe_gather(_ptr(x), x.stride(0), _ptr(offs), _ptr(sel_e), _ptr(sel_w), _ptr(sel_rank), T, int(top), W, si,
+                                  _ptr(xs), _ptr(row_dst), _ptr(row_w), _stream()), "moe_gather")
+        hidden = ctx.alloc((padded, F), x.dtype)
+        _check(L.prism_moe_gemm_tcgen05(_ptr(xs), W, _ptr(gate_up_w), _ptr(offs), _ptr(counts), None, None, ntok, tiles, E, F, W,
+                                        1, MOE_ACTS[act], _ptr(hidden), F, _ptr(err), _stream()), "moe_gemm_tcgen05")
+        y = ctx.alloc((top, T, W), torch.float32)
+        _check(L.prism_moe_gemm_tcgen05(_ptr(hidden), F, _ptr(down_w), _ptr(offs), _ptr(counts), _ptr(row_dst),
+                                        None if scale_input else _ptr(row_w), ntok, tiles, E, W, F, 0, 0, _ptr(y), W, _ptr(err),
+                                        _stream()), "moe_gemm_tcgen05")
+        return y
     ints = torch.empty(E + (E + 1) + 4 * rows, dtype=torch.int32, device=dev)
     counts, offs = ints[:E], ints[E:2 * E + 1]
     o = 2 * E + 1
@@ -1811,13 +1846,11 @@ def moe_feed_forward(ctx, x: torch.Tensor, logits: torch.Tensor, gate_up_w: torc
     counts.zero_()
     flt = torch.empty(2 * rows, dtype=torch.float32, device=dev)
     sel_w, row_w = flt[:rows], flt[rows:]
-    L = lib()
     _check(L.prism_moe_route(_ptr(logits), logits.stride(0), T, E, int(top), 1 if softmax else 0, 1 if renorm else 0,
                              _ptr(counts), _ptr(sel_e), _ptr(sel_w), _ptr(sel_rank), _stream()), "moe_route")
-    _check(L.prism_moe_place(_ptr(counts), _ptr(sel_e), _ptr(sel_w), _ptr(sel_rank), T, E, int(top), _ptr(offs), _ptr(row_tok),
+    _check(L.prism_moe_place(_ptr(counts), _ptr(sel_e), _ptr(sel_w), _ptr(sel_rank), T, E, int(top), 1, _ptr(offs), _ptr(row_tok),
                              _ptr(row_w), _ptr(row_dst), _stream()), "moe_place")
     hidden = ctx.alloc((rows, F), x.dtype)
-    si = 1 if scale_input else 0
     _check(L.prism_moe_gemm(_ptr(x), x.stride(0), _ptr(gate_up_w), _dt(x), _ptr(offs), _ptr(row_tok), _ptr(row_w), _ptr(row_dst),
                             rows, E, F, W, 1, si, MOE_ACTS[act], _ptr(hidden), F, _stream()), "moe_gemm")
     y = ctx.alloc((top, T, W), torch.float32)

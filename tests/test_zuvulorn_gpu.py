@@ -463,7 +463,7 @@ def plain_experts(x, logits, gu, dn, top, F):
 
 
 @pytest.mark.parametrize("T, W, F, E, top", [(1, 72, 24, 6, 2), (37, 64, 40, 3, 1), (130, 128, 96, 8, 3), (5, 33, 7, 5, 5), (9, 16, 8, 1, 1),
-                                             (300, 64, 32, 64, 2), (2, 256, 64, 16, 1)])
+                                             (300, 64, 32, 64, 2), (2, 256, 64, 16, 1), (700, 256, 200, 5, 2), (20, 136, 328, 4, 2)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_experts_take_their_tokens_scaled_by_the_score(T, W, F, E, top, dtype):
     """Scores spread by a large router, so that the choice does not hang on rounding; every choice of a token is a
@@ -491,6 +491,32 @@ def test_experts_take_their_tokens_scaled_by_the_score(T, W, F, E, top, dtype):
             a = x[t].float()
             ref2[t] += wgt * ((ZP.silu(a @ gu[e, :F].float().T) * (a @ gu[e, F:].float().T)).to(dtype).float() @ dn[e].float().T)
     assert float((y2.sum(0).cpu() - ref2).abs().max()) <= tol * max(1.0, float(ref2.abs().max()))
+
+
+@pytest.mark.parametrize("T, W, F, E, top", [(3, 64, 24, 4, 2), (33, 192, 136, 6, 3), (64, 128, 128, 2, 2), (65, 128, 72, 9, 1),
+                                             (500, 320, 264, 7, 2)])
+def test_experts_on_tensor_cores_against_cuda_cores(T, W, F, E, top):
+    """bf16: tiles of one expert each on the tensor cores against the CUDA-core kernels on the same choice; experts
+    without a token, stretches that end inside a tile, feature counts that are no multiple of the tile."""
+    from prism_b200 import ops
+    g = torch.Generator().manual_seed(T * 7 + E)
+    x = torch.randn(T, W, generator=g).to(torch.bfloat16).to(DEV)
+    logits = (torch.randn(T, E, generator=g) * 2.0).to(DEV)
+    if E > 2:
+        logits[:, 1] = -30.0                     # nobody chooses expert 1
+    gu = (torch.randn(E, 2 * F, W, generator=g) / W ** 0.5).to(torch.bfloat16).to(DEV)
+    dn = (torch.randn(E, W, F, generator=g) / F ** 0.5).to(torch.bfloat16).to(DEV)
+    ctx = step_ctx([T], [0])
+    assert ops.lib().prism_moe_tcgen05_supported(W, F)
+    for kw in (dict(), dict(softmax=True, renorm=True, scale_input=False, act="gelu_tanh")):
+        ops.moe_tensor_cores = False
+        try:
+            ref = ops.moe_feed_forward(ctx, x, logits, gu, dn, top, **kw).clone()
+        finally:
+            ops.moe_tensor_cores = True
+        got = ops.moe_feed_forward(ctx, x, logits, gu, dn, top, **kw)
+        ops.check_tc_errors()
+        assert float((got - ref).abs().max()) <= 2e-2 * max(1.0, float(ref.abs().max()))
 
 
 # ---------------------------------------------------------------------------------------------------------
