@@ -428,6 +428,7 @@ def zuvulorn_kernel_numbers(s, pk, once=None):
         run(f"delta_scan_{label}", lambda: ops.recurrent_scan(ops.SCAN_DELTA, x[:, :G * dk], x[:, G * dk:2 * G * dk], x[:, 2 * G * dk:],
                                                               state, c, H, rep, dk, dv, o, bg=bg), flops, nbytes, fp32=True)
     # the real-gated recurrence: gates (two block-diagonal products, float32) and the scan per channel
+    actx = types.SimpleNamespace(alloc=lambda shape, dtype: torch.empty(shape, dtype=dtype, device=DEV))
     C, nb = W, W // 128
     bs = C // nb
     wr, wi = (torch.randn(nb, bs, bs, device=DEV, dtype=torch.bfloat16) / bs ** 0.5 for _ in range(2))
@@ -436,7 +437,8 @@ def zuvulorn_kernel_numbers(s, pk, once=None):
     for label, batch, cached, q_len in shapes:
         Tt = batch * q_len
         c = types.SimpleNamespace(seg_start=(torch.arange(batch + 1, dtype=torch.int32) * q_len).to(DEV),
-                                  state_slots=torch.arange(batch, dtype=torch.int32, device=DEV), S=batch)
+                                  state_slots=torch.arange(batch, dtype=torch.int32, device=DEV), S=batch, max_q_len=q_len,
+                                  alloc=actx.alloc)
         u, y = torch.randn(Tt, C, device=DEV), torch.randn(Tt, C, device=DEV)
         ag = torch.empty(2, Tt, C, device=DEV)
         st = torch.zeros(batch + 1, C, device=DEV)

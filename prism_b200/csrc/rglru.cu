@@ -163,6 +163,97 @@ __global__ void rglru_scan_kernel(const float* __restrict__ a_in, const float* _
     *st = S;
 }
 
+// The same recurrence for long stretches, in two launches.  A request's tokens are cut into chunks of L; chunk k of
+// request i keeps its results in row  seg_start[i] / L + i + k  of ws [rows, 2, C] (no two requests share a row).
+//   pass 1, per chunk and channel:  A = product of a,  B = the chunk's last S when it starts from 0;  chunk 0 also
+//                                   saves the state the request came with (ws0 [S, C]).
+//   pass 2, per chunk and channel:  S = the saved state, carried over the chunks before this one (S <- A S + B),
+//                                   then the chunk itself, token after token; the last chunk leaves the state.
+// grid (channel blocks, chunks of the longest request, requests).
+template <int L>
+__global__ void rglru_chunk_kernel(const float* __restrict__ a_in, const float* __restrict__ g_in, long long as,
+                                   const float* __restrict__ state_in, const int* __restrict__ seg_start,
+                                   const int* __restrict__ slots, int C, float* __restrict__ ws, float* __restrict__ ws0) {
+    pdl_trigger();
+    pdl_wait();
+    const float* a = pdl_fresh(a_in);
+    const float* g = pdl_fresh(g_in);
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int seg = blockIdx.z, s0 = seg_start[seg], s1 = seg_start[seg + 1];
+    const int t0 = s0 + blockIdx.y * L;
+    if (t0 >= s1) return;
+    const int t1 = min(s1, t0 + L);
+    if (blockIdx.y == 0) ws0[(size_t)seg * C + c] = pdl_fresh(state_in)[(size_t)slots[seg] * C + c];
+    float A = 1.f, B = 0.f;
+    int t = t0;
+    for (; t + 4 <= t1; t += 4) {
+        float av[4], gv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            av[j] = a[(size_t)(t + j) * as + c];
+            gv[j] = g[(size_t)(t + j) * as + c];
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            A *= av[j];
+            B = fmaf(av[j], B, gv[j]);
+        }
+    }
+    for (; t < t1; ++t) {
+        const float av = a[(size_t)t * as + c];
+        A *= av;
+        B = fmaf(av, B, g[(size_t)t * as + c]);
+    }
+    float* w = ws + ((size_t)(s0 / L + seg + blockIdx.y) * 2) * C + c;
+    w[0] = A;
+    w[C] = B;
+}
+
+template <typename T, int L>
+__global__ void rglru_apply_kernel(const float* __restrict__ a_in, const float* __restrict__ g_in, long long as,
+                                   const float* __restrict__ y_in, long long ys, float* __restrict__ state,
+                                   const int* __restrict__ seg_start, const int* __restrict__ slots, int C, int act,
+                                   const float* __restrict__ ws_in, const float* __restrict__ ws0_in, T* __restrict__ out,
+                                   long long os) {
+    pdl_trigger();
+    pdl_wait();
+    const float* a = pdl_fresh(a_in);
+    const float* g = pdl_fresh(g_in);
+    const float* y = pdl_fresh(y_in);
+    const float* ws = pdl_fresh(ws_in);
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int seg = blockIdx.z, s0 = seg_start[seg], s1 = seg_start[seg + 1];
+    const int t0 = s0 + blockIdx.y * L;
+    if (t0 >= s1) return;
+    const int t1 = min(s1, t0 + L);
+    float S = pdl_fresh(ws0_in)[(size_t)seg * C + c];
+    const float* w = ws + ((size_t)(s0 / L + seg) * 2) * C + c;
+    for (int k = 0; k < (int)blockIdx.y; ++k, w += 2 * (size_t)C) S = fmaf(w[0], S, w[C]);
+    int t = t0;
+    for (; t + 4 <= t1; t += 4) {
+        float av[4], gv[4], yv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            av[j] = a[(size_t)(t + j) * as + c];
+            gv[j] = g[(size_t)(t + j) * as + c];
+            yv[j] = y[(size_t)(t + j) * ys + c];
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            S = fmaf(av[j], S, gv[j]);
+            out[(size_t)(t + j) * os + c] = from_float<T>(S * (act ? rg_gelu_tanh(yv[j]) : yv[j]));
+        }
+    }
+    for (; t < t1; ++t) {
+        S = fmaf(a[(size_t)t * as + c], S, g[(size_t)t * as + c]);
+        const float yv = y[(size_t)t * ys + c];
+        out[(size_t)t * os + c] = from_float<T>(S * (act ? rg_gelu_tanh(yv) : yv));
+    }
+    if (t1 == s1) state[(size_t)slots[seg] * C + c] = S;
+}
+
 }  // namespace prism
 
 PRISM_EXPORT int prism_causal_conv(const float* x, long long x_stride, const void* taps, int taps_dtype, const void* bias,
@@ -219,4 +310,30 @@ PRISM_EXPORT int prism_rglru_scan(const float* a, const float* g, long long ag_s
                                          y, y_stride, state, seg_start, slots, C, act, (__nv_bfloat16*)out, out_stride);
     return (int)prism::launch_kernel(prism::rglru_scan_kernel<float>, grid, dim3(threads), 0, stream, a, g, ag_stride, y,
                                      y_stride, state, seg_start, slots, C, act, (float*)out, out_stride);
+}
+
+#define PRISM_RGLRU_CHUNK 64
+
+// The chunked form for long stretches: longest = the longest request's tokens in this step (an upper bound will do);
+// ws: float32 [T / 64 + S + 1, 2, C], ws0: float32 [S, C].
+PRISM_EXPORT int prism_rglru_scan_chunked(const float* a, const float* g, long long ag_stride, const float* y,
+                                          long long y_stride, float* state, const int* seg_start, const int* slots, int S,
+                                          int C, int longest, int act, float* ws, float* ws0, void* out, int out_dtype,
+                                          long long out_stride, cudaStream_t stream) {
+    if (S <= 0 || C <= 0 || longest <= 0) return 0;
+    constexpr int L = PRISM_RGLRU_CHUNK;
+    const int chunks = (longest + L - 1) / L;
+    if (S > 65535 || chunks > 65535) return (int)cudaErrorInvalidValue;
+    const int threads = 64;
+    dim3 grid((C + threads - 1) / threads, chunks, S);
+    int rc = (int)prism::launch_kernel(prism::rglru_chunk_kernel<L>, grid, dim3(threads), 0, stream, a, g, ag_stride,
+                                       (const float*)state, seg_start, slots, C, ws, ws0);
+    if (rc) return rc;
+    if (out_dtype == PRISM_DTYPE_BF16)
+        return (int)prism::launch_kernel(prism::rglru_apply_kernel<__nv_bfloat16, L>, grid, dim3(threads), 0, stream, a, g,
+                                         ag_stride, y, y_stride, state, seg_start, slots, C, act, (const float*)ws,
+                                         (const float*)ws0, (__nv_bfloat16*)out, out_stride);
+    return (int)prism::launch_kernel(prism::rglru_apply_kernel<float, L>, grid, dim3(threads), 0, stream, a, g, ag_stride, y,
+                                     y_stride, state, seg_start, slots, C, act, (const float*)ws, (const float*)ws0,
+                                     (float*)out, out_stride);
 }

@@ -106,6 +106,7 @@ class _Sig:
     prism_recurrent_scan = [_i, _p, _ll, _ll, _ll, _ll, _p, _p, _ll, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _i, _p]
     prism_decay_from_exponent = [_p, _ll, _p, _i, _i, _i, _p]
     prism_lowrank_decay = [_p, _ll, _i, _p, _p, _i, _i, _i, _p, _ll, _i, _i, _p, _i, _i, _p]
+    prism_rglru_scan_chunked = [_p, _p, _ll, _p, _ll, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p, _i, _ll, _p]
     prism_moe_route = [_p, _ll, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p]
     prism_moe_place = [_p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p]
     prism_moe_tcgen05_supported = [_i, _i]
@@ -1772,6 +1773,9 @@ def block_gates(u: torch.Tensor, wr: torch.Tensor, wi: torch.Tensor, br: torch.T
            "block_gates")
 
 
+RGLRU_CHUNKED_FROM = 128       # a request's tokens in one step from which the scan runs in chunks (csrc/rglru.cu)
+
+
 def rglru_scan(a: torch.Tensor, g: torch.Tensor, y: torch.Tensor, state: torch.Tensor, ctx, out: torch.Tensor,
                gelu: bool = True):
     """``S <- a S + g`` per channel, token after token of each request of the step, from and into ``state [slots, C]``
@@ -1782,6 +1786,16 @@ def rglru_scan(a: torch.Tensor, g: torch.Tensor, y: torch.Tensor, state: torch.T
     assert a.dtype == g.dtype == y.dtype == torch.float32 and a.stride(1) == g.stride(1) == y.stride(1) == 1
     assert g.shape == (T, C) and y.shape == (T, C) and a.stride(0) == g.stride(0) and out.shape == (T, C) and out.stride(1) == 1
     assert state.dtype == torch.float32 and state.is_contiguous() and state[0].numel() == C
+    longest = int(getattr(ctx, "max_q_len", None) or T)
+    if longest >= RGLRU_CHUNKED_FROM:
+        # long stretches: chunks of 64 tokens side by side, their carries combined afterwards (two launches)
+        ws = ctx.alloc((T // 64 + ctx.S + 1, 2, C), torch.float32)
+        ws0 = ctx.alloc((ctx.S, C), torch.float32)
+        _check(lib().prism_rglru_scan_chunked(_ptr(a), _ptr(g), a.stride(0), _ptr(y), y.stride(0), _ptr(state),
+                                              _ptr(ctx.seg_start), _ptr(ctx.state_slots), ctx.S, C, longest, 1 if gelu else 0,
+                                              _ptr(ws), _ptr(ws0), _ptr(out), _dt(out), out.stride(0), _stream()),
+               "rglru_scan_chunked")
+        return
     _check(lib().prism_rglru_scan(_ptr(a), _ptr(g), a.stride(0), _ptr(y), y.stride(0), _ptr(state), _ptr(ctx.seg_start),
                                   _ptr(ctx.state_slots), ctx.S, C, 1 if gelu else 0, _ptr(out), _dt(out), out.stride(0),
                                   _stream()), "rglru_scan")

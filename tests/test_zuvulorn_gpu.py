@@ -165,6 +165,47 @@ def test_block_gates_and_the_recurrence_in_pieces(blocks, bs, wdt):
     assert float((state[1] - 9.0).abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("C", [5, 64, 200])
+def test_long_stretches_of_the_recurrence_run_in_chunks(C):
+    """Requests of unequal length in one step, some longer than the size from which the scan runs in chunks (ends at
+    a chunk's last token, one past it, one short of it), from states that are not zero, into slots in any order;
+    then one more token each from the states left."""
+    from prism_b200 import ops
+    qlens = [300, 1, 128, 129, 127, 64, 513]
+    slots = [3, 0, 6, 1, 5, 2, 4]
+    g = torch.Generator().manual_seed(C)
+    T = sum(qlens)
+    a = torch.rand(T, C, generator=g) * 0.5 + 0.5
+    a[10:200] = 1.0 - 1e-4 * torch.rand(190, C, generator=g)          # a long memory across several chunks
+    b = torch.randn(T, C, generator=g)
+    y = torch.randn(T, C, generator=g)
+    st0 = torch.randn(7, C, generator=g)
+    want = torch.zeros(T, C, dtype=torch.float64)
+    last = torch.zeros(7, C, dtype=torch.float64)
+    at = 0
+    for n, sl in zip(qlens, slots):
+        S = st0[sl].double()
+        for t in range(at, at + n):
+            S = a[t].double() * S + b[t].double()
+            want[t] = S * y[t].double()
+        last[sl] = S
+        at += n
+    ctx = step_ctx(qlens, slots)
+    assert ctx.max_q_len >= ops.RGLRU_CHUNKED_FROM
+    state = st0.clone().to(DEV)
+    out = torch.empty(T, C, device=DEV)
+    ops.rglru_scan(a.to(DEV), b.to(DEV), y.to(DEV), state, ctx, out, gelu=False)
+    scale = float(want.abs().max())
+    assert float((out.cpu().double() - want).abs().max()) <= 2e-5 * scale
+    assert float((state.cpu().double() - last).abs().max()) <= 2e-5 * float(last.abs().max())
+    # the chunks' form against the token-by-token kernel on the same step
+    state2 = st0.clone().to(DEV)
+    out2 = torch.empty(T, C, device=DEV)
+    ctx.max_q_len = 1
+    ops.rglru_scan(a.to(DEV), b.to(DEV), y.to(DEV), state2, ctx, out2, gelu=False)
+    assert float((out2 - out).abs().max()) <= 2e-5 * scale
+
+
 @pytest.mark.parametrize("G, rep, dk, dv", [(2, 2, 12, 20), (1, 1, 1, 1), (1, 3, 7, 5), (3, 1, 64, 32), (1, 2, 128, 128), (1, 1, 300, 16)])
 def test_delta_rule_with_a_decay_per_key_channel_in_pieces(G, rep, dk, dv):
     """Decay, error against the decayed state, write, then the read-out that sees the write; two requests of unequal
