@@ -33,7 +33,10 @@ __device__ __forceinline__ float moe_tc_act(float z, int act) {
 template <int NTOK, bool DUAL> struct MoeCfg {
     static constexpr int W_TILES = DUAL ? 2 : 1;
     static constexpr int STAGE_BYTES = W_TILES * MOE_TILE_M * TILE_K * 2 + NTOK * TILE_K * 2;
-    static constexpr int FIT = 200 * 1024 / STAGE_BYTES;
+    // the down product of a prompt's tiles (K = an expert's inner width: few k-blocks, 64 rows to scatter): a short ring,
+    // so that three CTAs share an SM and one's store hides behind the others' products; decode steps stream weights
+    // and keep the deep ring
+    static constexpr int FIT = ((DUAL || NTOK < 64) ? 200 : 72) * 1024 / STAGE_BYTES;
     static constexpr int STAGES = FIT >= 6 ? 6 : (FIT >= 2 ? FIT : 2);
     static constexpr int TMEM_COLS = (W_TILES * NTOK) <= 32 ? 32 : ((W_TILES * NTOK) <= 64 ? 64 : 128);
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
