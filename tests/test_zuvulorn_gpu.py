@@ -566,7 +566,7 @@ def test_experts_on_tensor_cores_against_cuda_cores(T, W, F, E, top):
 
 LIMIT = {"float32": 3e-5, "bfloat16": 4e-2}
 ILL = {"float32": 0.0, "bfloat16": 0.05}        # see zuvulorn_helpers.judge
-LENGTHS = {"A": [1, 9, 40, 71, 130], "B": [2, 65, 128, 200, 333], "C": [1, 5, 33], "D": [3, 26, 61], "E": [1, 20, 70]}
+LENGTHS = {"A": [1, 9, 40, 71, 130], "B": [2, 65, 128, 200, 333], "C": [1, 5, 33], "D": [3, 26, 61], "E": [1, 20, 70], "F": [3, 70, 150, 257]}
 
 
 def runner_for(folder, dtype, max_tokens, page_size, max_live=4):
@@ -586,7 +586,7 @@ def served(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "small_portions", "mixed"])
 def test_cutting(name, dtype, mode):
     """Whole prompts, a decoded tail, portions (one schedule of twos and threes only), and mixed batches of up

@@ -94,7 +94,17 @@ CONFIG_D = model(77, 52, streams=None, layers=[
 CONFIG_E = model(90, 48, streams=4, layers=[layer("rglru", rglru(64, 4, 4), experts(32, 4, 1)),
                                             layer("channel_delta", delta(6, 3, 8, 8, 3, 4, 4), None),
                                             layer("rglru", rglru(24, 2, 2), None)])
-CONFIGS = {"A": (CONFIG_A, 11, 8), "B": (CONFIG_B, 12, 64), "C": (CONFIG_C, 13, 16), "D": (CONFIG_D, 14, 8),
+# F: a few hundred wide, sizes the tensor-core kernels take throughout but none a power of two times another: heads of
+# 128 with values of 64 and half a head rotated, four of twelve experts, inner widths of 72 and 136 (no multiple of a
+# k-block), values wider than keys in the delta rule, four copies, the layer on another's keys without feed-forward
+CONFIG_F = model(500, 320, streams=4, eps=1e-5, layers=[
+    layer("rglru", rglru(384, 3, 2), experts(72, 12, 4)),
+    layer("channel_delta", delta(4, 2, 64, 128, 4, 24, 40), experts(136, 5, 2)),
+    layer("attention", attn(8, 2, 128, 64, scale=0.05, rot_dims=64, base=8000.0, scaling=(8.0, 1.0, 4.0, 128)), experts(72, 12, 4)),
+    layer("attention", attn(8, 2, 128, 64, scale=0.07, rot_dims=64, base=8000.0, scaling=(8.0, 1.0, 4.0, 128), kv_from=2), None),
+    layer("attention", attn(4, 4, 32, 32, scale=0.2, rot_dims=32, base=1000.0), experts(40, 3, 3)),
+])
+CONFIGS = {"F": (CONFIG_F, 16, 64), "A": (CONFIG_A, 11, 8), "B": (CONFIG_B, 12, 64), "C": (CONFIG_C, 13, 16), "D": (CONFIG_D, 14, 8),
            "E": (CONFIG_E, 15, 16)}      # config, seed, page size
 
 
