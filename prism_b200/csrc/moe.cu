@@ -3,6 +3,7 @@
 //   lower index wins a tie); the weight of a choice is its score, optionally divided by the sum of the chosen.
 // The (token, choice) pairs are sorted by expert on the device, so that each expert's rows are one stretch:
 //   prism_moe_route    top-k per token; counts[e] rows per expert, and each pair's rank among its expert's rows
+//   prism_moe_route_place  both of the above in one CTA, for a step of few tokens
 //   prism_moe_place    offs = prefix sums of counts (each rounded up to `pad`); per sorted row: its token, its weight,
 //                      and where its result goes
 //   prism_moe_gemm     grouped product over the sorted rows, expert by expert, no host knowledge of the counts:
@@ -23,19 +24,11 @@ __device__ __forceinline__ float moe_act(float z, int act) {
     return fmaxf(z, 0.f);                                                                             // relu
 }
 
-// One warp per token.  logits [T, E] float32 (row stride ls).  sel_e, sel_w, sel_rank [T, top].
-__global__ void moe_route_kernel(const float* __restrict__ logits_in, long long ls, int T, int E, int top, int softmax,
-                                 int renorm, int* __restrict__ counts, int* __restrict__ sel_e, float* __restrict__ sel_w,
-                                 int* __restrict__ sel_rank) {
-    pdl_trigger();
-    pdl_wait();
-    const float* logits = pdl_fresh(logits_in);
-    extern __shared__ float sc[];                       // [warps][E]
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (t >= T) return;
-    float* s = sc + (size_t)warp * E;
-    const float* z = logits + (size_t)t * ls;
+// One warp takes a token: scores into s [E] (shared), the `top` largest chosen (the lower index wins a tie), counts
+// [E] (shared or global) raised by one per choice, whose old value is the choice's rank among its expert's rows.
+__device__ __forceinline__ void moe_route_token(const float* __restrict__ z, float* s, int E, int top, int softmax, int renorm,
+                                                int lane, int* counts, int* __restrict__ sel_e, float* __restrict__ sel_w,
+                                                int* __restrict__ sel_rank) {
     float mx = -INFINITY;
     for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
     mx = warp_max(mx);
@@ -63,15 +56,72 @@ __global__ void moe_route_kernel(const float* __restrict__ logits_in, long long 
         const float w = softmax ? best / den : best;
         chosen += w;
         if (lane == 0) {
-            sel_e[(size_t)t * top + j] = at;
-            sel_w[(size_t)t * top + j] = w;
-            sel_rank[(size_t)t * top + j] = atomicAdd(counts + at, 1);
+            sel_e[j] = at;
+            sel_w[j] = w;
+            sel_rank[j] = atomicAdd(counts + at, 1);
             s[at] = -INFINITY;
         }
         __syncwarp();
     }
     if (renorm && lane == 0)
-        for (int j = 0; j < top; ++j) sel_w[(size_t)t * top + j] /= chosen;
+        for (int j = 0; j < top; ++j) sel_w[j] /= chosen;
+}
+
+// One warp per token.  logits [T, E] float32 (row stride ls).  sel_e, sel_w, sel_rank [T, top].
+__global__ void moe_route_kernel(const float* __restrict__ logits_in, long long ls, int T, int E, int top, int softmax,
+                                 int renorm, int* __restrict__ counts, int* __restrict__ sel_e, float* __restrict__ sel_w,
+                                 int* __restrict__ sel_rank) {
+    pdl_trigger();
+    pdl_wait();
+    const float* logits = pdl_fresh(logits_in);
+    extern __shared__ float sc[];                       // [warps][E]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= T) return;
+    moe_route_token(logits + (size_t)t * ls, sc + (size_t)warp * E, E, top, softmax, renorm, lane, counts,
+                    sel_e + (size_t)t * top, sel_w + (size_t)t * top, sel_rank + (size_t)t * top);
+}
+
+// A step of few tokens (decode) in one CTA and one launch: the counters start at zero in shared memory, a warp routes
+// every eighth token, then the offsets (stretches padded to `pad`) and, unless row_tok is null, the sorted rows.
+__global__ void moe_route_place_kernel(const float* __restrict__ logits_in, long long ls, int T, int E, int top, int softmax,
+                                       int renorm, int pad, int* __restrict__ counts_out, int* __restrict__ offs,
+                                       int* __restrict__ sel_e, float* __restrict__ sel_w, int* __restrict__ sel_rank,
+                                       int* __restrict__ row_tok, float* __restrict__ row_w, int* __restrict__ row_dst) {
+    pdl_trigger();
+    extern __shared__ float sc[];                       // [warps][E] floats, then counts [E] and offsets [E + 1]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    int* cnt = reinterpret_cast<int*>(sc + (size_t)warps * E);
+    int* so = cnt + E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    pdl_wait();
+    const float* logits = pdl_fresh(logits_in);
+    __syncthreads();
+    for (int t = warp; t < T; t += warps)
+        moe_route_token(logits + (size_t)t * ls, sc + (size_t)warp * E, E, top, softmax, renorm, lane, cnt,
+                        sel_e + (size_t)t * top, sel_w + (size_t)t * top, sel_rank + (size_t)t * top);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int e = 0; e < E; ++e) {
+            so[e] = acc;
+            acc += (cnt[e] + pad - 1) / pad * pad;
+        }
+        so[E] = acc;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+        offs[e] = so[e];
+        if (e < E) counts_out[e] = cnt[e];
+    }
+    if (row_tok == nullptr) return;
+    for (int i = threadIdx.x; i < T * top; i += blockDim.x) {
+        const int t = i / top, j = i - t * top;
+        const int p = so[sel_e[i]] + sel_rank[i];
+        row_tok[p] = t;
+        row_w[p] = sel_w[i];
+        row_dst[p] = j * T + t;
+    }
 }
 
 // offs [E + 1]: every expert's stretch starts at a multiple of pad; row_tok, row_w, row_dst in sorted order (at the
@@ -238,6 +288,20 @@ PRISM_EXPORT int prism_moe_route(const float* logits, long long logits_stride, i
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return (int)prism::launch_kernel(kern, dim3((T + warps - 1) / warps), dim3(32 * warps), smem, stream, logits, logits_stride,
                                      T, E, top, softmax, renorm, counts, sel_e, sel_w, sel_rank);
+}
+
+// prism_moe_route and prism_moe_place (and the counters' reset) in one launch of one CTA, for steps of few tokens.
+PRISM_EXPORT int prism_moe_route_place(const float* logits, long long logits_stride, int T, int E, int top, int softmax,
+                                       int renorm, int pad, int* counts, int* offs, int* sel_e, float* sel_w, int* sel_rank,
+                                       int* row_tok, float* row_w, int* row_dst, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (E < 1 || top < 1 || top > E || pad < 1) return (int)cudaErrorInvalidValue;
+    const int warps = 8;
+    const size_t smem = (size_t)warps * E * sizeof(float) + (size_t)(2 * E + 1) * sizeof(int);
+    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    return (int)prism::launch_kernel(prism::moe_route_place_kernel, dim3(1), dim3(32 * warps), smem, stream, logits,
+                                     logits_stride, T, E, top, softmax, renorm, pad, counts, offs, sel_e, sel_w, sel_rank,
+                                     row_tok, row_w, row_dst);
 }
 
 PRISM_EXPORT int prism_moe_place(const int* counts, const int* sel_e, const float* sel_w, const int* sel_rank, int T, int E,

@@ -109,6 +109,7 @@ class _Sig:
     prism_rglru_scan_chunked = [_p, _p, _ll, _p, _ll, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p, _i, _ll, _p]
     prism_moe_route = [_p, _ll, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p]
     prism_moe_place = [_p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p]
+    prism_moe_route_place = [_p, _ll, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p]
     prism_moe_tcgen05_supported = [_i, _i]
     prism_moe_gather = [_p, _ll, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p, _p]
     prism_moe_gemm_tcgen05 = [_p, _ll, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _ll, _p, _p]
@@ -1805,6 +1806,23 @@ MOE_ACTS = {"silu": 0, "gelu_tanh": 1, "relu": 2}      # csrc/moe.cu: moe_act
 moe_tensor_cores = True                                 # bf16 experts on tcgen05 (csrc/moe_tcgen05.cu); False: CUDA cores
 
 
+MOE_ONE_CTA_TOKENS = 16       # steps of up to this many tokens are routed and placed by one CTA in one launch (a warp a token at a time: 64 tokens take longer than the three launches)
+
+
+def _moe_route_place(L, logits, T, E, top, softmax, renorm, pad, counts, offs, sel_e, sel_w, sel_rank, row_tok, row_w, row_dst):
+    sm, rn = 1 if softmax else 0, 1 if renorm else 0
+    if T <= MOE_ONE_CTA_TOKENS and 8 * E * 4 + (2 * E + 1) * 4 <= 48 * 1024:
+        _check(L.prism_moe_route_place(_ptr(logits), logits.stride(0), T, E, int(top), sm, rn, int(pad), _ptr(counts), _ptr(offs),
+                                       _ptr(sel_e), _ptr(sel_w), _ptr(sel_rank), _ptr(row_tok), _ptr(row_w), _ptr(row_dst),
+                                       _stream()), "moe_route_place")
+        return
+    counts.zero_()
+    _check(L.prism_moe_route(_ptr(logits), logits.stride(0), T, E, int(top), sm, rn, _ptr(counts), _ptr(sel_e), _ptr(sel_w),
+                             _ptr(sel_rank), _stream()), "moe_route")
+    _check(L.prism_moe_place(_ptr(counts), _ptr(sel_e), _ptr(sel_w), _ptr(sel_rank), T, E, int(top), int(pad), _ptr(offs),
+                             _ptr(row_tok), _ptr(row_w), _ptr(row_dst), _stream()), "moe_place")
+
+
 def moe_feed_forward(ctx, x: torch.Tensor, logits: torch.Tensor, gate_up_w: torch.Tensor, down_w: torch.Tensor, top: int,
                      softmax: bool = False, renorm: bool = False, scale_input: bool = True, act: str = "silu") -> torch.Tensor:
     """Mixture of experts on the step's rows: ``x [T, W]`` (compute dtype), router ``logits [T, E]`` float32,
@@ -1834,14 +1852,10 @@ def moe_feed_forward(ctx, x: torch.Tensor, logits: torch.Tensor, gate_up_w: torc
         counts, offs = ints[:E], ints[E:2 * E + 1]
         o = 2 * E + 1
         sel_e, sel_rank, row_dst = ints[o:o + rows], ints[o + rows:o + 2 * rows], ints[o + 2 * rows:]
-        counts.zero_()
         flt = torch.empty(rows + padded, dtype=torch.float32, device=dev)
         sel_w, row_w = flt[:rows], flt[rows:]
         err = _tc_err_word(dev)
-        _check(L.prism_moe_route(_ptr(logits), logits.stride(0), T, E, int(top), 1 if softmax else 0, 1 if renorm else 0,
-                                 _ptr(counts), _ptr(sel_e), _ptr(sel_w), _ptr(sel_rank), _stream()), "moe_route")
-        _check(L.prism_moe_place(_ptr(counts), _ptr(sel_e), _ptr(sel_w), _ptr(sel_rank), T, E, int(top), ntok, _ptr(offs), None,
-                                 None, None, _stream()), "moe_place")
+        _moe_route_place(L, logits, T, E, top, softmax, renorm, ntok, counts, offs, sel_e, sel_w, sel_rank, None, None, None)
         xs = ctx.alloc((padded, W), x.dtype)
         _check(L.prism_moe_gather(_ptr(x), x.stride(0), _ptr(offs), _ptr(sel_e), _ptr(sel_w), _ptr(sel_rank), T, int(top), W, si,
                                   _ptr(xs), _ptr(row_dst), _ptr(row_w), _stream()), "moe_gather")
@@ -1857,13 +1871,9 @@ def moe_feed_forward(ctx, x: torch.Tensor, logits: torch.Tensor, gate_up_w: torc
     counts, offs = ints[:E], ints[E:2 * E + 1]
     o = 2 * E + 1
     sel_e, sel_rank, row_tok, row_dst = (ints[o + i * rows:o + (i + 1) * rows] for i in range(4))
-    counts.zero_()
     flt = torch.empty(2 * rows, dtype=torch.float32, device=dev)
     sel_w, row_w = flt[:rows], flt[rows:]
-    _check(L.prism_moe_route(_ptr(logits), logits.stride(0), T, E, int(top), 1 if softmax else 0, 1 if renorm else 0,
-                             _ptr(counts), _ptr(sel_e), _ptr(sel_w), _ptr(sel_rank), _stream()), "moe_route")
-    _check(L.prism_moe_place(_ptr(counts), _ptr(sel_e), _ptr(sel_w), _ptr(sel_rank), T, E, int(top), 1, _ptr(offs), _ptr(row_tok),
-                             _ptr(row_w), _ptr(row_dst), _stream()), "moe_place")
+    _moe_route_place(L, logits, T, E, top, softmax, renorm, 1, counts, offs, sel_e, sel_w, sel_rank, row_tok, row_w, row_dst)
     hidden = ctx.alloc((rows, F), x.dtype)
     _check(L.prism_moe_gemm(_ptr(x), x.stride(0), _ptr(gate_up_w), _dt(x), _ptr(offs), _ptr(row_tok), _ptr(row_w), _ptr(row_dst),
                             rows, E, F, W, 1, si, MOE_ACTS[act], _ptr(hidden), F, _stream()), "moe_gemm")
