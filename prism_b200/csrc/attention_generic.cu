@@ -57,6 +57,8 @@ __host__ __device__ __forceinline__ int mask_first_key(int kind, int size, int p
 // differ in size and live in planes with strides of their own (elements between tokens' rows and between
 // heads), so that the values may also be a slice of the key rows.  `sink` (per query head, or null): one more
 // term exp(sink_h) in the softmax's denominator, with no value; it is not multiplied by `scale`.
+// `dist_bias` (float32 [nh, dist_max + 1], or null): a bias by distance, added to the scaled score of the key
+// n = pos - j positions back: dist_bias[h][min(n, dist_max)] (distances beyond the table's end share its last entry).
 template <typename T, int MAXD>
 __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, int q_head_stride, T* __restrict__ out,
                                     int out_stride, const T* __restrict__ kc, long long k_row_stride, int k_head_stride,
@@ -65,7 +67,8 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, int q
                                     int bt_width, const int* __restrict__ positions,
                                     const int* __restrict__ tok_seg, int Ttot, int nh, int nkv,
                                     int dk, int dv, int page_size, int num_pages, int mask_kind, int mask_size,
-                                    int mask_keep, float scale, const void* __restrict__ sink, int sink_bf16, int* err) {
+                                    int mask_keep, float scale, const void* __restrict__ sink, int sink_bf16, int* err,
+                                    const float* __restrict__ dist_bias, int dist_max) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
@@ -117,6 +120,7 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, int q
                 for (int d = 0; d < dk; ++d) dot += qs[d] * to_float(kr[d]);
             }
             s = dot * scale;
+            if (dist_bias != nullptr) s += dist_bias[(size_t)h * (dist_max + 1) + min(pos - j, dist_max)];
         }
         const float m_new = fmaxf(m, warp_max(s));
         if (m_new == -INFINITY) continue;            // only after a page error
@@ -161,7 +165,7 @@ static int launch_generic(const void* q, int q_stride, int q_head_stride, void* 
                           int v_head_stride, const int* block_table, int bt_width, const int* positions,
                           const int* tok_seg, int T_, int nh, int nkv, int dk, int dv, int page_size, int num_pages,
                           int mask_kind, int mask_size, int mask_keep, float scale, const void* sink, int sink_bf16,
-                          int* err, cudaStream_t stream) {
+                          int* err, const float* dist_bias, int dist_max, cudaStream_t stream) {
     const int warps = 4;
     const long long total = (long long)T_ * nh;
     const int blocks = (int)((total + warps - 1) / warps);
@@ -171,7 +175,7 @@ static int launch_generic(const void* q, int q_stride, int q_head_stride, void* 
     kern<<<blocks, warps * 32, smem, stream>>>(
         (const T*)q, q_stride, q_head_stride, (T*)out, out_stride, (const T*)kc, k_row_stride, k_head_stride,
         (const T*)vc, v_row_stride, v_head_stride, block_table, bt_width, positions, tok_seg, T_, nh, nkv, dk, dv,
-        page_size, num_pages, mask_kind, mask_size, mask_keep, scale, sink, sink_bf16, err);
+        page_size, num_pages, mask_kind, mask_size, mask_keep, scale, sink, sink_bf16, err, dist_bias, dist_max);
     return (int)cudaPeekAtLastError();
 }
 
@@ -180,7 +184,7 @@ static int launch_generic(const void* q, int q_stride, int q_head_stride, void* 
 // Keys of dk and values of dv entries, each plane with its own strides (in elements: between the rows of
 // consecutive cache slots, and between kv heads); mask_kind PRISM_MASK_*; mask_keep: under PRISM_MASK_WINDOW
 // the first mask_keep positions stay visible to every later query; sink: per-head float32 or bf16
-// (sink_dtype) or null.  Returns cudaErrorInvalidValue for dv > 1024 or dk > 12288 / warps.
+// (sink_dtype) or null; dist_bias: float32 [nh, dist_max + 1] or null.  Returns cudaErrorInvalidValue for dv > 1024 or dk > 12288 / warps.
 PRISM_EXPORT int prism_attention_masked_generic(const void* q, int q_stride, int q_head_stride, void* out,
                                                 int out_stride, const void* kc, long long k_row_stride,
                                                 int k_head_stride, const void* vc, long long v_row_stride,
@@ -188,8 +192,10 @@ PRISM_EXPORT int prism_attention_masked_generic(const void* q, int q_stride, int
                                                 const int* positions, const int* tok_seg, int T, int nh, int nkv,
                                                 int dk, int dv, int page_size, int num_pages, int mask_kind,
                                                 int mask_size, int mask_keep, float scale, const void* sink,
-                                                int sink_dtype, int* err, cudaStream_t stream) {
+                                                int sink_dtype, int* err, const float* dist_bias, int dist_max,
+                                                cudaStream_t stream) {
     if (T <= 0) return 0;
+    if (dist_bias != nullptr && dist_max < 0) return (int)cudaErrorInvalidValue;
     if (mask_keep < 0 || (mask_keep > 0 && mask_kind != PRISM_MASK_WINDOW)) return (int)cudaErrorInvalidValue;
     if (dv > 1024 || dv <= 0 || dk <= 0 || dk > 8192 || nkv <= 0 || nh % nkv != 0) return (int)cudaErrorInvalidValue;
     const int sb = sink_dtype == PRISM_DTYPE_BF16;
@@ -197,7 +203,7 @@ PRISM_EXPORT int prism_attention_masked_generic(const void* q, int q_stride, int
     return prism::launch_generic<TT, MD>(q, q_stride, q_head_stride, out, out_stride, kc, k_row_stride,             \
                                          k_head_stride, vc, v_row_stride, v_head_stride, block_table, bt_width,     \
                                          positions, tok_seg, T, nh, nkv, dk, dv, page_size, num_pages, mask_kind,   \
-                                         mask_size, mask_keep, scale, sink, sb, err, stream)
+                                         mask_size, mask_keep, scale, sink, sb, err, dist_bias, dist_max, stream)
     if (dtype == PRISM_DTYPE_BF16) {
         if (dv <= 256) PRISM_GENERIC(__nv_bfloat16, 8);
         if (dv <= 512) PRISM_GENERIC(__nv_bfloat16, 16);
@@ -222,5 +228,5 @@ PRISM_EXPORT int prism_attention_generic(const void* q, int q_stride, void* out,
                                           (long long)nkv * hd, hd, dtype, block_table, bt_width, positions, tok_seg,
                                           T, nh, nkv, hd, hd, page_size, num_pages,
                                           window > 0 ? PRISM_MASK_WINDOW : PRISM_MASK_CAUSAL, window, 0, scale, nullptr, 0,
-                                          err, stream);
+                                          err, nullptr, 0, stream);
 }

@@ -1,7 +1,8 @@
 // bf16 paged attention on tensor cores for layers that the equal-size causal kernels (attention_bf16.cu) do
 // not cover: keys of dk and values of dv entries per head (dv != dk allowed, and the values may be the leading
 // entries of the key rows themselves), a key mask of any PRISM_MASK_* kind, and an optional sink in the
-// softmax's denominator.
+// softmax's denominator, and an optional bias by distance (a float32 table [nh, dist_max + 1]: the key n positions
+// back gets table[h][min(n, dist_max)] added to its scaled score).
 //
 // A CTA takes one segment, one kv head and 64 rows; a row is a (query token, query head of that kv head)
 // pair, so the nh / nkv heads that share a kv head sit side by side and every key/value tile is read once
@@ -69,6 +70,8 @@ struct MaskedAttn {
     int nsplit;        // few-rows shape: CTAs that share one (segment, kv head)'s key tiles
     float* part_o;     // [segments, nh, nsplit, dv]   their partial outputs (not normalised) ...
     float* part_ml;    // [segments, nh, nsplit, 2]    ... with running maximum (log2 domain) and sum
+    const float* dist_bias;   // [nh, dist_max + 1] or null: added to the scaled score of the key min(p - key, dist_max) back
+    int dist_max;
 };
 
 __device__ __forceinline__ int ma_first_key(int kind, int size, int pos) {
@@ -205,11 +208,13 @@ attn_masked_kernel(const MaskedAttn a) {
     // the two rows this thread holds scores of
     int p_row[2], lo_row[2];
     bool ok_row[2];
+    const float* bias_row[2];
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
         const int r = rowbase + (lane >> 2) + e * 8;
         const int tk = r / a.rpt, hh = r - tk * a.rpt;
         ok_row[e] = tk < ntok && hh < nheads;
+        bias_row[e] = a.dist_bias != nullptr ? a.dist_bias + (size_t)(head0 + (hh < nheads ? hh : 0)) * (a.dist_max + 1) : nullptr;
         p_row[e] = pos0 + (tk < ntok ? tk : ntok - 1);
         lo_row[e] = ma_first_key(a.mask_kind, a.mask_size, p_row[e]);
     }
@@ -247,7 +252,7 @@ attn_masked_kernel(const MaskedAttn a) {
             const int key0 = kfirst + (lane & 3) * 2;
             float mx[2] = {-INFINITY, -INFINITY};
             // only a tile that crosses some row's first or last visible key (or a warp with unused rows) needs the mask
-            if (!w_all_rows || kfirst < w_lo_last || klast > pos0 + w_tk0) {
+            if (a.dist_bias != nullptr || !w_all_rows || kfirst < w_lo_last || klast > pos0 + w_tk0) {
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -255,7 +260,11 @@ attn_masked_kernel(const MaskedAttn a) {
                         const int key = key0 + nt * 8 + (e & 1);
                         const int rr = e >> 1;
                         const bool vis = ok_row[rr] && key <= p_row[rr] && (key >= lo_row[rr] || key < a.mask_keep);
-                        const float v = vis ? s[nt][e] * a.scale_log2 : -INFINITY;
+                        float v = -INFINITY;
+                        if (vis) {
+                            v = s[nt][e] * a.scale_log2;
+                            if (bias_row[rr] != nullptr) v += bias_row[rr][min(p_row[rr] - key, a.dist_max)] * 1.4426950408889634f;
+                        }
                         s[nt][e] = v;
                         mx[rr] = fmaxf(mx[rr], v);
                     }
@@ -468,7 +477,7 @@ PRISM_EXPORT int prism_attention_masked_bf16(const void* q, long long q_stride, 
                                              int nh, int nkv, int dk, int dv, int page_size, int num_pages,
                                              int mask_kind, int mask_size, int mask_keep, float scale,
                                              const void* sink, int sink_dtype, int few_rows, int nsplit, float* part_o, float* part_ml,
-                                             int* err, cudaStream_t stream) {
+                                             int* err, const float* dist_bias, int dist_max, cudaStream_t stream) {
     using namespace prism;
     if (S <= 0 || max_q_len <= 0) return 0;
     if (!prism_attention_masked_supported(dk, dv, nh, nkv)) return (int)cudaErrorInvalidValue;
@@ -500,6 +509,8 @@ PRISM_EXPORT int prism_attention_masked_bf16(const void* q, long long q_stride, 
     a.nsplit = few_rows ? nsplit : 1;
     a.part_o = part_o;
     a.part_ml = part_ml;
+    a.dist_bias = dist_bias;
+    a.dist_max = dist_bias != nullptr && dist_max >= 0 ? dist_max : 0;
 #define PRISM_MA_LAUNCH(DVP)                                                                                        \
     do {                                                                                                            \
         if (v_in_k) return few_rows ? launch_masked<DVP, true, true>(a, S, max_q_len, stream)                       \

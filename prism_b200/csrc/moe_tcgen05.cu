@@ -13,6 +13,7 @@
 //
 //   dual:   hidden[p, n] = act(gate_e a_p)[n] * (up_e a_p)[n]   bf16, p the padded row; W is [E, 2 N, K]
 //   single: y[dst[p], n] = (down_e h_p)[n] (* weight[p])         float32; W is [E, N, K]
+//           without dst: hidden[p, n] = act(up_e a_p)[n]         bf16: the hidden layer of experts without a gate
 //
 // A decode step (a few rows per expert) reads every chosen expert's weights once; a prompt's tiles of one expert
 // re-read them from L2.  Every mbarrier wait is bounded, as in gemm_tcgen05.cu.
@@ -27,7 +28,8 @@ constexpr int MOE_THREADS = 192;
 __device__ __forceinline__ float moe_tc_act(float z, int act) {
     if (act == 0) return z / (1.f + expf(-z));                                                      // silu
     if (act == 1) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));   // gelu_tanh
-    return fmaxf(z, 0.f);                                                                             // relu
+    const float r = fmaxf(z, 0.f);
+    return act == 3 ? r * r : r;                                                                      // relu squared, relu
 }
 
 template <int NTOK, bool DUAL> struct MoeCfg {
@@ -166,6 +168,8 @@ moe_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     if (DUAL) {
                         reinterpret_cast<__nv_bfloat16*>(y)[(size_t)p * ldy + m] =
                             __float2bfloat16_rn(moe_tc_act(acc[0][n], act) * acc[W_TILES - 1][n]);
+                    } else if (row_dst == nullptr) {          // an expert without a gate: its hidden layer, act(up a_p)
+                        reinterpret_cast<__nv_bfloat16*>(y)[(size_t)p * ldy + m] = __float2bfloat16_rn(moe_tc_act(acc[0][n], act));
                     } else {
                         const float v = row_w != nullptr ? acc[0][n] * row_w[p] : acc[0][n];
                         reinterpret_cast<float*>(y)[(size_t)row_dst[p] * ldy + m] = v;
@@ -244,7 +248,8 @@ PRISM_EXPORT int prism_moe_gather(const void* x, long long ldx, const int* offs,
 
 // a [x_rows, K] bf16 in padded order (x_rows = token_tiles * ntok); w [E, (2) N, K] bf16 contiguous.
 // dual 1: out [x_rows, N] bf16 (row stride ldo), out[p] = act(gate a_p) * (up a_p).
-// dual 0: out float32, out[row_dst[p]] = w a_p (times row_w[p] if row_w is given).
+// dual 0: out float32, out[row_dst[p]] = w a_p (times row_w[p] if row_w is given); row_dst null: out [x_rows, N] bf16,
+// out[p] = act(w a_p).
 PRISM_EXPORT int prism_moe_gemm_tcgen05(const void* a, long long lda, const void* w, const int* offs, const int* counts,
                                         const int* row_dst, const float* row_w, int ntok, int token_tiles, int E, int N,
                                         int K, int dual, int act, void* out, long long ldo, int* err, cudaStream_t stream) {

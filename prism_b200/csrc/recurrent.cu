@@ -7,6 +7,9 @@
 //       S <- diag(w) S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
 //   decayed outer-product sum with a bonus for the current token (SCAN_BONUS), w, u vectors over the key channels:
 //       o = (S + diag(u) k v^T)^T r;   S <- diag(w) S + k v^T                    (the read-out sees S before the write)
+//   generalized delta rule (SCAN_GENERAL), w, e, c vectors over the key channels (e the unit key, c = a * e a removal
+//   rate per channel times it):
+//       S <- diag(w) S - c (e^T S) + k v^T;   o = S^T r         (decay and removal both read the state before the token)
 //
 // Everything that enters the recurrence is float32: the kernels here read the float32 results of the input
 // projections, and the state never leaves float32.  A request's state lives in its slot between steps, so
@@ -27,6 +30,7 @@
 #define PRISM_SCAN_DELTA 0
 #define PRISM_SCAN_BONUS 1
 #define PRISM_SCAN_CHANNEL 2
+#define PRISM_SCAN_GENERAL 3
 
 namespace prism {
 
@@ -147,16 +151,19 @@ __global__ void decay_from_exponent_kernel(float* __restrict__ w, long long ws, 
 //   PRISM_LR_EXPEXP    exp(-exp(z))                          a per-channel decay from its double exponent
 //   PRISM_LR_SOFTPLUS  exp(-exp(alog[n / per]) softplus(z))  a per-channel decay with one rate per group of `per` channels
 //   PRISM_LR_SIGMOID   sigmoid(z)                            a gate
+//   PRISM_LR_EXPSIG    exp(-rate sigmoid(z))                 a per-channel decay kept inside (exp(-rate), 1), rate a constant
 // b may be null.  A CTA takes 128 channels and sixteen tokens, so that every weight it reads serves sixteen tokens
 // (whose inner values sit side by side in shared memory: four 128-bit loads per weight); w2t is the second matrix
 // transposed, [R, N], so that neighbouring threads read neighbouring floats.
 #define PRISM_LR_EXPEXP 0
 #define PRISM_LR_SOFTPLUS 1
 #define PRISM_LR_SIGMOID 2
+#define PRISM_LR_EXPSIG 3
 constexpr int LRD_TOK = 16;
 __global__ void lowrank_decay_kernel(const float* __restrict__ low_in, long long ls, int R, const float* __restrict__ w2t,
                                      const void* __restrict__ w0, int w0_bf16, int N, int T, float* __restrict__ out,
-                                     long long os, int inner, int epi, const void* __restrict__ alog, int alog_bf16, int per) {
+                                     long long os, int inner, int epi, const void* __restrict__ alog, int alog_bf16, int per,
+                                     float crate) {
     pdl_trigger();
     pdl_wait();
     const float* low = pdl_fresh(low_in);
@@ -190,8 +197,35 @@ __global__ void lowrank_decay_kernel(const float* __restrict__ low_in, long long
         if (t0 + j < T) {
             const float z = acc[j] + b;
             out[(size_t)(t0 + j) * os + n] = epi == PRISM_LR_EXPEXP ? expf(-expf(z))
-                                             : epi == PRISM_LR_SOFTPLUS ? expf(-rate * softplus_f(z)) : sigmoid_f(z);
+                                             : epi == PRISM_LR_SOFTPLUS ? expf(-rate * softplus_f(z))
+                                             : epi == PRISM_LR_EXPSIG ? expf(-crate * sigmoid_f(z)) : sigmoid_f(z);
         }
+}
+
+// ex[t][h dk + i] = e_i = k_i / sqrt(sum_i k_i^2 + unit_eps) per head (the unit key), and
+// ex[t][(H + h) dk + i] = sigmoid(a_i + ab[h dk + i]) e_i (the removal rate per channel times it): what the generalized
+// delta rule takes out of its state.  k, a: float32 column blocks of one product (row stride ps).  One warp per (token, head).
+__global__ void unit_removal_kernel(const float* __restrict__ k_in, const float* __restrict__ a_in, long long ps,
+                                    const void* __restrict__ ab, int ab_bf16, float unit_eps, int Ttot, int H, int dk,
+                                    float* __restrict__ ex) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w >= (long long)Ttot * H) return;
+    const int t = (int)(w / H), h = (int)(w % H);
+    const float* k = pdl_fresh(k_in) + (size_t)t * ps + (size_t)h * dk;
+    const float* a = pdl_fresh(a_in) + (size_t)t * ps + (size_t)h * dk;
+    float ss = 0.f;
+    for (int i = lane; i < dk; i += 32) ss += k[i] * k[i];
+    ss = warp_sum(ss);
+    const float inv = 1.f / sqrtf(ss + unit_eps);
+    float* e = ex + (size_t)t * 2 * H * dk + (size_t)h * dk;
+    for (int i = lane; i < dk; i += 32) {
+        const float u = k[i] * inv;
+        e[i] = u;
+        e[(size_t)H * dk + i] = sigmoid_f(a[i] + (ab != nullptr ? load_param(ab, ab_bf16, (size_t)h * dk + i) : 0.f)) * u;
+    }
 }
 
 // out[t][h dv + c] = o[t][h][c] / sqrt(mean_c(o[t][h]^2) + eps) * weight[widx] * act(gate[t][h dv + c]) * scale,
@@ -234,6 +268,7 @@ __global__ void headnorm_gate_kernel(const float* __restrict__ o_in, const float
 //   SCAN_BONUS:  r at qo + h dk, k at ko + h dk, v at vo + h dv, the decay's exponent ww [T, H dk] (row stride ws)
 //                with w = exp(-exp(ww + w0)) formed in shared memory, w0 [H dk], bonus u [H dk].
 //   SCAN_CHANNEL: q, k, v as for SCAN_DELTA; the decay itself in ww [T, H dk] (row stride ws); bg [T, H]: beta.
+//   SCAN_GENERAL: r, k, v as for SCAN_BONUS; the decay itself in ww; ex [T, 2 H dk]: the unit key e at h dk, c at (H + h) dk.
 // ---------------------------------------------------------------------------------------------------------
 struct ScanArgs {
     const float* x;          // q | k | v (or r | k | v) rows
@@ -246,6 +281,8 @@ struct ScanArgs {
     int w0_bf16;
     const void* u;
     int u_bf16;
+    const float* ex;         // GENERAL: unit key | removal rate times unit key, [T, 2 H dk] (row stride es)
+    long long es;
     float* state;            // [slots, H, dv, dk]
     const int* seg_start;
     const int* slots;
@@ -276,7 +313,7 @@ __global__ void scan_kernel(const ScanArgs a) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float sm[];
-    constexpr int NV = MODE == PRISM_SCAN_DELTA ? 2 : 3;       // vectors over the key channels per token
+    constexpr int NV = MODE == PRISM_SCAN_DELTA ? 2 : (MODE == PRISM_SCAN_GENERAL ? 5 : 3);       // vectors over the key channels per token
     constexpr int Q = R / 4;                                   // quads of rows a thread owns
     const int h = blockIdx.x, seg = blockIdx.y, col0 = blockIdx.z * a.cols;
     const int s0 = a.seg_start[seg], qlen = a.seg_start[seg + 1] - s0;
@@ -299,6 +336,7 @@ __global__ void scan_kernel(const ScanArgs a) {
     const float* x = pdl_fresh(a.x);
     const float* bg = pdl_fresh(a.bg);
     const float* ww = pdl_fresh(a.ww);
+    const float* ex = pdl_fresh(a.ex);
 
     // padding entries of the staging buffers (rows beyond dk that the column's threads cover, columns beyond the
     // CTA's) are never written by the copies: zero them once
@@ -323,7 +361,7 @@ __global__ void scan_kernel(const ScanArgs a) {
         float* dst0 = sm + (size_t)buf * TB * per_tok;
         const int unit = a.vec ? 4 : 1;
         const int nk = (dk + unit - 1) / unit, nc = (ncols + unit - 1) / unit;     // pieces per vector
-        const size_t head_q = (size_t)(MODE == PRISM_SCAN_BONUS ? h : kvh) * dk;
+        const size_t head_q = (size_t)((MODE == PRISM_SCAN_BONUS || MODE == PRISM_SCAN_GENERAL) ? h : kvh) * dk;
         for (int tt = 0; tt < nb; ++tt) {
             const size_t t = (size_t)(s0 + b0 + tt);
             const float* xr = x + t * a.xs;
@@ -332,6 +370,10 @@ __global__ void scan_kernel(const ScanArgs a) {
                 cp_async_f(dst + c * unit, xr + a.qo + head_q + c * unit, unit);
                 cp_async_f(dst + dkp + c * unit, xr + a.ko + head_q + c * unit, unit);
                 if (MODE != PRISM_SCAN_DELTA) cp_async_f(dst + 2 * dkp + c * unit, ww + t * a.ws + (size_t)h * dk + c * unit, unit);
+                if (MODE == PRISM_SCAN_GENERAL) {
+                    cp_async_f(dst + 3 * dkp + c * unit, ex + t * a.es + (size_t)h * dk + c * unit, unit);
+                    cp_async_f(dst + 4 * dkp + c * unit, ex + t * a.es + (size_t)(a.H + h) * dk + c * unit, unit);
+                }
             }
             for (int c = lane; c < nc; c += 32)
                 cp_async_f(dst + NV * dkp + c * unit, xr + a.vo + (size_t)h * dv + col0 + c * unit, unit);
@@ -462,6 +504,36 @@ __global__ void scan_kernel(const ScanArgs a) {
                     o2 += S[4 * m + 2] * qq.z;
                     o3 += S[4 * m + 3] * qq.w;
                 }
+            } else if (MODE == PRISM_SCAN_GENERAL) {
+                const float* wd = f2 + dkp;            // decay | unit key | removal times unit key | v
+                const float* ue = wd + dkp;
+                const float* ce = ue + dkp;
+                const float v = ce[dkp + lc];
+                float k0 = 0.f, k1 = 0.f, k2 = 0.f, k3 = 0.f;
+#pragma unroll
+                for (int m = 0; m < Q; ++m) {
+                    const float4 e4 = *reinterpret_cast<const float4*>(ue + 4 * (part + L * m));
+                    k0 += S[4 * m] * e4.x;
+                    k1 += S[4 * m + 1] * e4.y;
+                    k2 += S[4 * m + 2] * e4.z;
+                    k3 += S[4 * m + 3] * e4.w;
+                }
+                float es = (k0 + k1) + (k2 + k3);
+                es = column_sum<L>(es);                // e^T S of this column, from the state before the token
+#pragma unroll
+                for (int m = 0; m < Q; ++m) {
+                    const int i = 4 * (part + L * m);
+                    const float4 rr = *reinterpret_cast<const float4*>(f1 + i), kk = *reinterpret_cast<const float4*>(f2 + i);
+                    const float4 w4 = *reinterpret_cast<const float4*>(wd + i), c4 = *reinterpret_cast<const float4*>(ce + i);
+                    S[4 * m] = w4.x * S[4 * m] - c4.x * es + kk.x * v;
+                    S[4 * m + 1] = w4.y * S[4 * m + 1] - c4.y * es + kk.y * v;
+                    S[4 * m + 2] = w4.z * S[4 * m + 2] - c4.z * es + kk.z * v;
+                    S[4 * m + 3] = w4.w * S[4 * m + 3] - c4.w * es + kk.w * v;
+                    o0 += S[4 * m] * rr.x;
+                    o1 += S[4 * m + 1] * rr.y;
+                    o2 += S[4 * m + 2] * rr.z;
+                    o3 += S[4 * m + 3] * rr.w;
+                }
             } else {
                 const float* wd = f2 + dkp;
                 const float v = wd[dkp + lc];
@@ -504,7 +576,7 @@ __global__ void scan_kernel(const ScanArgs a) {
 
 template <int MODE, int R, int L>
 static int launch_scan(const ScanArgs& a, int S, cudaStream_t stream) {
-    const int per_tok = (MODE == PRISM_SCAN_DELTA ? 2 : 3) * a.dkp + a.colsp + 4;
+    const int per_tok = (MODE == PRISM_SCAN_DELTA ? 2 : (MODE == PRISM_SCAN_GENERAL ? 5 : 3)) * a.dkp + a.colsp + 4;
     const size_t smem = ((size_t)3 * a.TB * per_tok + (MODE == PRISM_SCAN_BONUS ? a.dkp : 0)) * sizeof(float);
     auto kern = scan_kernel<MODE, R, L>;
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
@@ -563,10 +635,10 @@ PRISM_EXPORT int prism_decay_from_exponent(float* w, long long w_stride, const v
 }
 
 // low [T, R] float32 (row stride free), w2t [R, N] float32, w0 [N] or null; out [T, N] float32; inner 1: tanh of low;
-// epi PRISM_LR_*; alog [N / per] for PRISM_LR_SOFTPLUS.
+// epi PRISM_LR_*; alog [N / per] for PRISM_LR_SOFTPLUS; crate: the constant rate of PRISM_LR_EXPSIG.
 PRISM_EXPORT int prism_lowrank_decay(const float* low, long long low_stride, int R, const float* w2t, const void* w0,
                                      int w0_dtype, int N, int T, float* out, long long out_stride, int inner, int epi,
-                                     const void* alog, int alog_dtype, int per, cudaStream_t stream) {
+                                     const void* alog, int alog_dtype, int per, float crate, cudaStream_t stream) {
     if (epi == PRISM_LR_SOFTPLUS && (alog == nullptr || per < 1)) return (int)cudaErrorInvalidValue;
     if (T <= 0 || N <= 0) return 0;
     const size_t smem = (size_t)prism::LRD_TOK * R * sizeof(float);
@@ -575,7 +647,17 @@ PRISM_EXPORT int prism_lowrank_decay(const float* low, long long low_stride, int
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return (int)prism::launch_kernel(kern, dim3((N + 127) / 128, (T + prism::LRD_TOK - 1) / prism::LRD_TOK), dim3(128), smem,
                                      stream, low, low_stride, R, w2t, w0, w0_dtype == PRISM_DTYPE_BF16, N, T, out, out_stride, inner, epi, alog,
-                                     alog_dtype == PRISM_DTYPE_BF16, per < 1 ? 1 : per);
+                                     alog_dtype == PRISM_DTYPE_BF16, per < 1 ? 1 : per, crate);
+}
+
+// k, a [T, H dk] float32 column blocks with row stride ps; ab [H dk] or null; ex [T, 2 H dk] float32 out.
+PRISM_EXPORT int prism_unit_removal(const float* k, const float* a, long long ps, const void* ab, int ab_dtype, float unit_eps,
+                                    int T, int H, int dk, float* ex, cudaStream_t stream) {
+    if (T <= 0 || H <= 0 || dk <= 0) return 0;
+    const int warps = 4;
+    const long long total = (long long)T * H;
+    return (int)prism::launch_kernel(prism::unit_removal_kernel, dim3((unsigned)((total + warps - 1) / warps)), dim3(warps * 32), 0,
+                                     stream, k, a, ps, ab, ab_dtype == PRISM_DTYPE_BF16, unit_eps, T, H, dk, ex);
 }
 
 PRISM_EXPORT int prism_headnorm_gate(const float* o, const float* gate, long long gate_stride, const void* weight,
@@ -600,7 +682,8 @@ PRISM_EXPORT int prism_recurrent_scan(int mode, const float* x, long long x_stri
                                       const float* bg,
                                       const float* ww, long long ww_stride, const void* w0, int w0_dtype, const void* u,
                                       int u_dtype, float* state, const int* seg_start, const int* slots, int S, int max_q_len,
-                                      int H, int rep, int dk, int dv, float* out, int w_ready, cudaStream_t stream) {
+                                      int H, int rep, int dk, int dv, float* out, int w_ready, const float* ex,
+                                      long long ex_stride, cudaStream_t stream) {
     using namespace prism;
     if (S <= 0) return 0;
     if (H < 1 || rep < 1 || dk < 1 || dv < 1 || dk > 1024 || S > 65535) return (int)cudaErrorInvalidValue;
@@ -609,6 +692,8 @@ PRISM_EXPORT int prism_recurrent_scan(int mode, const float* x, long long x_stri
     a.w0 = w0; a.w0_bf16 = w0_dtype == PRISM_DTYPE_BF16; a.u = u; a.u_bf16 = u_dtype == PRISM_DTYPE_BF16;
     a.state = state; a.seg_start = seg_start; a.slots = slots; a.out = out; a.H = H; a.rep = rep; a.dk = dk; a.dv = dv;
     a.w_ready = w_ready;
+    a.ex = ex; a.es = ex_stride;
+    if (mode == PRISM_SCAN_GENERAL && (ex == nullptr || ww == nullptr || rep != 1)) return (int)cudaErrorInvalidValue;
     // A token's work is one chain (dot product, shuffles, update, dot product, shuffles), so a CTA is latency
     // bound: eight threads a column, four warps of them side by side, and as many CTAs as there are column blocks.
     const int R = dk <= 32 ? 4 : (dk <= 64 ? 8 : (dk <= 128 ? 16 : 32));
@@ -627,8 +712,9 @@ PRISM_EXPORT int prism_recurrent_scan(int mode, const float* x, long long x_stri
     a.colsp = (cols + 3) / 4 * 4;
     a.vec = dk % 4 == 0 && dv % 4 == 0 && cols % 4 == 0 && x_stride % 4 == 0 && qo % 4 == 0 && ko % 4 == 0 && vo % 4 == 0 &&
             (uintptr_t)x % 16 == 0 && (uintptr_t)state % 16 == 0 &&
-            (mode == PRISM_SCAN_DELTA || (ww_stride % 4 == 0 && (uintptr_t)ww % 16 == 0));
-    const int per_tok = (mode == PRISM_SCAN_DELTA ? 2 : 3) * a.dkp + a.colsp + 4;
+            (mode == PRISM_SCAN_DELTA || (ww_stride % 4 == 0 && (uintptr_t)ww % 16 == 0)) &&
+            (mode != PRISM_SCAN_GENERAL || (ex_stride % 4 == 0 && (uintptr_t)ex % 16 == 0 && ((long long)H * dk) % 4 == 0));
+    const int per_tok = (mode == PRISM_SCAN_DELTA ? 2 : (mode == PRISM_SCAN_GENERAL ? 5 : 3)) * a.dkp + a.colsp + 4;
     int tb = (24 * 1024 / 4) / per_tok;
     tb = tb < 1 ? 1 : (tb > 16 ? 16 : tb);
     a.TB = tb > max_q_len ? (max_q_len < 1 ? 1 : max_q_len) : tb;      // a decode step stages one token, and CTAs are small
@@ -645,6 +731,7 @@ PRISM_EXPORT int prism_recurrent_scan(int mode, const float* x, long long x_stri
     if (mode == PRISM_SCAN_DELTA) PRISM_SCAN(PRISM_SCAN_DELTA);
     if (mode == PRISM_SCAN_BONUS) PRISM_SCAN(PRISM_SCAN_BONUS);
     if (mode == PRISM_SCAN_CHANNEL) PRISM_SCAN(PRISM_SCAN_CHANNEL);
+    if (mode == PRISM_SCAN_GENERAL) PRISM_SCAN(PRISM_SCAN_GENERAL);
 #undef PRISM_SCAN
     return (int)cudaErrorInvalidValue;
 }

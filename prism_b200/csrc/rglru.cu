@@ -19,11 +19,14 @@ __device__ __forceinline__ float rg_gelu_tanh(float z) {
     return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
-// out[t][c] = bias[c] + sum_j taps[c][K-1-j] x[t-j][c]; x [T, *] float32 with row stride xs; tail [slots, K-1, C].
+// out[t][c] = bias[c] + sum_j taps[c][K-1-j] x[t-j][c] (+ x[t][c] with add_input: a convolution beside a skip path);
+// x [T, *] float32 with row stride xs; tail [slots, K-1, C]; out float32 or the compute dtype (rounded once).
+template <typename TO>
 __global__ void causal_conv_kernel(const float* __restrict__ x_in, long long xs, const void* __restrict__ taps, int taps_bf16,
                                    const void* __restrict__ bias, int bias_bf16, int K, int C, float* tail,
                                    const int* __restrict__ tok_seg, const int* __restrict__ seg_start,
-                                   const int* __restrict__ slots, float* __restrict__ out, long long os, int move_tail) {
+                                   const int* __restrict__ slots, TO* __restrict__ out, long long os, int move_tail,
+                                   int add_input) {
     pdl_trigger();
     pdl_wait();
     const float* x = pdl_fresh(x_in);
@@ -37,7 +40,8 @@ __global__ void causal_conv_kernel(const float* __restrict__ x_in, long long xs,
             const float v = src >= 0 ? x[(size_t)(t - j) * xs + c] : tl[(size_t)(K - 1 + src) * C + c];
             acc += load_param(taps, taps_bf16, (size_t)c * K + (K - 1 - j)) * v;
         }
-        out[(size_t)t * os + c] = acc;
+        if (add_input) acc += x[(size_t)t * xs + c];
+        out[(size_t)t * os + c] = from_float<TO>(acc);
         if (move_tail && K > 1) {          // one token per request: this thread is the only reader of its channel's tail
             for (int r = 0; r + 2 < K; ++r) tl[(size_t)r * C + c] = tl[(size_t)(r + 1) * C + c];
             tl[(size_t)(K - 2) * C + c] = x[(size_t)t * xs + c];
@@ -258,16 +262,20 @@ __global__ void rglru_apply_kernel(const float* __restrict__ a_in, const float* 
 
 PRISM_EXPORT int prism_causal_conv(const float* x, long long x_stride, const void* taps, int taps_dtype, const void* bias,
                                    int bias_dtype, int K, int C, float* tail, const int* tok_seg, const int* seg_start,
-                                   const int* slots, int T, float* out, long long out_stride, int move_tail,
-                                   cudaStream_t stream) {
+                                   const int* slots, int T, void* out, int out_dtype, long long out_stride, int move_tail,
+                                   int add_input, cudaStream_t stream) {
     if (T <= 0 || C <= 0) return 0;
     if (K < 1) return (int)cudaErrorInvalidValue;
     const int threads = 128;
     int gy = (C + threads - 1) / threads;
     if (gy > 64) gy = 64;
-    return (int)prism::launch_kernel(prism::causal_conv_kernel, dim3(T, gy), dim3(threads), 0, stream, x, x_stride, taps,
+    if (out_dtype == PRISM_DTYPE_BF16)
+        return (int)prism::launch_kernel(prism::causal_conv_kernel<__nv_bfloat16>, dim3(T, gy), dim3(threads), 0, stream, x,
+                                         x_stride, taps, taps_dtype == PRISM_DTYPE_BF16, bias, bias_dtype == PRISM_DTYPE_BF16, K, C,
+                                         tail, tok_seg, seg_start, slots, (__nv_bfloat16*)out, out_stride, move_tail, add_input);
+    return (int)prism::launch_kernel(prism::causal_conv_kernel<float>, dim3(T, gy), dim3(threads), 0, stream, x, x_stride, taps,
                                      taps_dtype == PRISM_DTYPE_BF16, bias, bias_dtype == PRISM_DTYPE_BF16, K, C, tail, tok_seg,
-                                     seg_start, slots, out, out_stride, move_tail);
+                                     seg_start, slots, (float*)out, out_stride, move_tail, add_input);
 }
 
 // u [T, blocks * bs] float32 (row stride u_stride); wr, wi [blocks, bs, bs] of w_dtype; br, bi [blocks * bs] of b_dtype;

@@ -195,6 +195,26 @@ __global__ void __launch_bounds__(1024) scale_add_rmsnorm_vec_kernel(float* __re
     }
 }
 
+// The residual sum alone, for a sublayer that reads the stream itself rather than its norm:
+//   residual[r, :] += sum_s delta[s, r, :]   (float32, in place);   copy[r, :] = residual[r, :] in the compute dtype.
+template <typename TD, typename TO>
+__global__ void add_rows_kernel(float* __restrict__ residual, const TD* __restrict__ delta_in, int nsplit, size_t split_stride,
+                                TO* __restrict__ copy, int H) {
+    pdl_trigger();
+    pdl_wait();
+    const TD* delta = pdl_fresh(delta_in);
+    const int r = blockIdx.x;
+    float* res = residual + (size_t)r * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = res[c];
+        if (delta != nullptr) {
+            for (int s = 0; s < nsplit; ++s) v += to_float(delta[(size_t)s * split_stride + (size_t)r * H + c]);
+            res[c] = v;
+        }
+        if (copy != nullptr) copy[(size_t)r * H + c] = from_float<TO>(v);
+    }
+}
+
 }  // namespace prism
 
 // x float32 [rows, H] in place; delta (null: none) [nsplit, rows, H] of delta_dtype; copy (null: none) [rows, H] of
@@ -260,4 +280,22 @@ PRISM_EXPORT int prism_add_rmsnorm(float* residual, const void* delta, int delta
 #undef LAUNCH
 #undef ARGS
     return (int)rc;
+}
+
+// residual [T, H] float32 += delta (nsplit planes [T, H] of delta_dtype, plane stride split_stride; null: nothing);
+// copy [T, H] of copy_dtype (null: none) receives the new rows.
+PRISM_EXPORT int prism_add_rows(float* residual, const void* delta, int delta_dtype, int nsplit, long long split_stride,
+                                void* copy, int copy_dtype, int T, int H, cudaStream_t stream) {
+    if (T <= 0 || H <= 0) return 0;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+#define PRISM_AR(TD, TO)                                                                                              \
+    return (int)prism::launch_kernel(prism::add_rows_kernel<TD, TO>, dim3(T), dim3(threads), 0, stream, residual,      \
+                                     (const TD*)delta, nsplit, (size_t)split_stride, (TO*)copy, H)
+    if (delta_dtype == PRISM_DTYPE_BF16) {
+        if (copy_dtype == PRISM_DTYPE_BF16) PRISM_AR(__nv_bfloat16, __nv_bfloat16);
+        PRISM_AR(__nv_bfloat16, float);
+    }
+    if (copy_dtype == PRISM_DTYPE_BF16) PRISM_AR(float, __nv_bfloat16);
+    PRISM_AR(float, float);
+#undef PRISM_AR
 }

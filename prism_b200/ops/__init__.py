@@ -81,7 +81,7 @@ _p, _i, _f, _ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlo
 
 
 class _Sig:
-    prism_embed = [_p, _p, _i, _p, _i, _i, _i, _f, _p, _p]
+    prism_embed = [_p, _p, _i, _p, _i, _i, _i, _f, _p, _p, _p, _p]
     prism_add_rmsnorm = [_p, _p, _i, _i, _ll, _p, _i, _f, _p, _i, _p, _i, _i, _p]
     prism_rope_table = [_p, _p, _i, _i, _p, _p]
     prism_rope_kv_write_partial = [_p, _i, _p, _i, _p, _i, _i, _p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i,
@@ -91,10 +91,10 @@ class _Sig:
     prism_attention_generic = [_p, _i, _p, _i, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i,
                                _i, _f, _p, _p]
     prism_attention_masked_generic = [_p, _i, _i, _p, _i, _p, _ll, _i, _p, _ll, _i, _i, _p, _i, _p, _p, _i, _i, _i,
-                                      _i, _i, _i, _i, _i, _i, _i, _f, _p, _i, _p, _p]
+                                      _i, _i, _i, _i, _i, _i, _i, _f, _p, _i, _p, _p, _i, _p]
     prism_attention_masked_supported = [_i, _i, _i, _i]
     prism_attention_masked_bf16 = [_p, _ll, _i, _p, _ll, _p, _ll, _i, _p, _ll, _i, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i,
-                                   _i, _i, _i, _i, _i, _f, _p, _i, _i, _i, _p, _p, _p, _p]
+                                   _i, _i, _i, _i, _i, _f, _p, _i, _i, _i, _p, _p, _p, _p, _i, _p]
     prism_scale_add_rmsnorm = [_p, _f, _p, _i, _i, _ll, _p, _i, _f, _p, _i, _i, _i, _p]
     prism_gated_product = [_p, _ll, _p, _ll, _p, _ll, _i, _i, _i, _i, _f, _i, _p]
     prism_qk_norm_rope_store = [_p, _p, _p, _ll, _p, _i, _p, _i, _f, _p, _i, _p, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i,
@@ -103,19 +103,20 @@ class _Sig:
     prism_state_tail = [_p, _ll, _i, _p, _i, _p, _p, _i, _p]
     prism_shift_mix = [_p, _i, _p, _p, _i, _i, _p, _p, _p, _i, _p, _i, _ll, _i, _p]
     prism_headnorm_gate = [_p, _p, _ll, _p, _i, _i, _f, _f, _i, _i, _i, _p, _i, _ll, _i, _p]
-    prism_recurrent_scan = [_i, _p, _ll, _ll, _ll, _ll, _p, _p, _ll, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _i, _p]
+    prism_recurrent_scan = [_i, _p, _ll, _ll, _ll, _ll, _p, _p, _ll, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _i, _p, _ll, _p]
+    prism_unit_removal = [_p, _p, _ll, _p, _i, _f, _i, _i, _i, _p, _p]
     prism_decay_from_exponent = [_p, _ll, _p, _i, _i, _i, _p]
-    prism_lowrank_decay = [_p, _ll, _i, _p, _p, _i, _i, _i, _p, _ll, _i, _i, _p, _i, _i, _p]
+    prism_lowrank_decay = [_p, _ll, _i, _p, _p, _i, _i, _i, _p, _ll, _i, _i, _p, _i, _i, _f, _p]
     prism_rglru_scan_chunked = [_p, _p, _ll, _p, _ll, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p, _i, _ll, _p]
-    prism_moe_route = [_p, _ll, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p]
+    prism_moe_route = [_p, _ll, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _i, _i, _i, _f, _f, _p]
     prism_moe_place = [_p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p]
-    prism_moe_route_place = [_p, _ll, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p]
+    prism_moe_route_place = [_p, _ll, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _f, _f, _p]
     prism_moe_tcgen05_supported = [_i, _i]
     prism_moe_gather = [_p, _ll, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _p, _p]
     prism_moe_gemm_tcgen05 = [_p, _ll, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _ll, _p, _p]
-    prism_moe_gemm = [_p, _ll, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _ll, _p]
+    prism_moe_gemm = [_p, _ll, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _ll, _i, _p]
     prism_hyper_norm = [_p, _ll, _p, _ll, _p, _i, _i, _ll, _p, _i, _p, _i, _p, _i, _i, _p, _i, _f, _i, _p, _i, _p, _i, _i, _p]
-    prism_causal_conv = [_p, _ll, _p, _i, _p, _i, _i, _i, _p, _p, _p, _p, _i, _p, _ll, _i, _p]
+    prism_causal_conv = [_p, _ll, _p, _i, _p, _i, _i, _i, _p, _p, _p, _p, _i, _p, _i, _ll, _i, _i, _p]
     prism_block_gates = [_p, _ll, _p, _p, _i, _p, _p, _i, _p, _i, _f, _i, _i, _i, _p, _p, _ll, _p]
     prism_rglru_scan = [_p, _p, _ll, _p, _ll, _p, _p, _p, _i, _i, _i, _p, _i, _ll, _p]
     prism_cache_store = [_p, _ll, _p, _i, _i, _p, _ll, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p]
@@ -123,6 +124,10 @@ class _Sig:
                              _p, _ll, _p]
     prism_rotate_slice = [_p, _ll, _i, _p, _ll, _i, _i, _i, _i, _p, _p, _i, _i, _p]
     prism_activation = [_p, _ll, _p, _ll, _i, _i, _i, _i, _p]
+    prism_glu = [_p, _ll, _p, _ll, _i, _i, _i, _i, _p]
+    prism_gather_gate = [_p, _ll, _p, _p, _i, _ll, _i, _i, _p, _i, _ll, _i, _i, _i, _p, _p]
+    prism_softcap = [_p, _ll, _f, _p]
+    prism_add_rows = [_p, _p, _i, _i, _ll, _p, _i, _i, _i, _p]
     prism_rms_rows = [_p, _ll, _p, _i, _f, _p, _ll, _i, _i, _i, _p]
     prism_attention_bf16_supported = [_i, _i, _i]
     prism_attention_decode_bf16 = [_p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f,
@@ -174,15 +179,21 @@ def _check(code: int, what: str):
 
 # --------------------------------------------------------------------------
 
-def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor, scale: float = 1.0):
-    """``out[t] = table[ids[t]] * scale`` as float32.  ids int32 [T]; table [V, H]."""
-    _cuda(ids, table, out)
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor, scale: float = 1.0,
+          positions: Optional[torch.Tensor] = None, sin_freq: Optional[torch.Tensor] = None):
+    """``out[t] = table[ids[t]] * scale`` as float32.  ids int32 [T]; table [V, H].  ``sin_freq`` (float32 ``[(H + 1) //
+    2]``) with ``positions`` (int32 ``[T]``): entry 2i of the row at position p also gets ``sin(p * sin_freq[i])`` and
+    entry 2i + 1 the cosine."""
+    _cuda(ids, table, out, positions, sin_freq)
+    if sin_freq is not None:
+        assert sin_freq.dtype == torch.float32 and sin_freq.is_contiguous() and sin_freq.shape[0] == (table.shape[1] + 1) // 2
+        assert positions is not None and positions.dtype == torch.int32 and positions.shape[0] == ids.shape[0]
     assert ids.dtype == torch.int32 and out.dtype == torch.float32
     assert table.is_contiguous() and out.is_contiguous()
     T, (V, H) = ids.shape[0], table.shape
     assert out.shape == (T, H)
     _check(lib().prism_embed(_ptr(ids), _ptr(table), _dt(table), _ptr(out), T, H, V, float(scale),
-                             _ptr(err), _stream()), "embed")
+                             _ptr(err), _ptr(positions) if sin_freq is not None else None, _ptr(sin_freq), _stream()), "embed")
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
@@ -1237,15 +1248,23 @@ def _plane_strides(plane: torch.Tensor):
     return plane.stride(1), plane.stride(2)
 
 
+def _check_dist_bias(dist_bias: Optional[torch.Tensor], nh: int):
+    if dist_bias is not None:
+        assert dist_bias.dtype == torch.float32 and dist_bias.is_contiguous() and dist_bias.dim() == 2
+        assert dist_bias.shape[0] == nh and dist_bias.shape[1] >= 1
+
+
 def attention_masked_generic(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
                              block_table: torch.Tensor, positions: torch.Tensor, tok_seg: torch.Tensor,
                              num_pages: int, mask: KeyMask, scale: float, sink: Optional[torch.Tensor],
-                             err: torch.Tensor):
+                             err: torch.Tensor, dist_bias: Optional[torch.Tensor] = None):
     """Shape-generic paged attention: ``q [T, nh, dk]`` (token and head strides free), keys ``[pages, P, nkv,
     dk]``, values ``[pages, P, nkv, dv]`` (may be a slice of the key plane), ``out [T, nh * dv]``; ``sink
     [nh]``: one more term ``exp(sink_h)`` in head h's softmax denominator.  float32 or bf16 storage, all
-    arithmetic float32."""
-    _cuda(q, out, k_plane, v_plane, block_table, positions, tok_seg, sink)
+    arithmetic float32.  ``dist_bias [nh, D + 1]`` float32: the key n positions back has ``dist_bias[h, min(n, D)]``
+    added to its scaled score."""
+    _cuda(q, out, k_plane, v_plane, block_table, positions, tok_seg, sink, dist_bias)
+    _check_dist_bias(dist_bias, q.shape[1])
     T, nh, dk = q.shape
     P, nkv, dv = k_plane.shape[1], k_plane.shape[2], v_plane.shape[3]
     assert k_plane.shape[3] == dk and v_plane.shape[:3] == k_plane.shape[:3]
@@ -1261,7 +1280,7 @@ def attention_masked_generic(q: torch.Tensor, out: torch.Tensor, k_plane: torch.
         out.stride(0) if T > 1 else nh * dv, _ptr(k_plane), krs, khs, _ptr(v_plane), vrs, vhs, _dt(q),
         _ptr(block_table), block_table.shape[1], _ptr(positions), _ptr(tok_seg), T, nh, nkv, dk, dv, P, num_pages,
         mask.kind, mask.size, mask.keep, float(scale), _ptr(sink), F32 if sink is None else _dt(sink), _ptr(err),
-        _stream()), "attention_masked_generic")
+        _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[1] - 1, _stream()), "attention_masked_generic")
 
 
 def cache_store(src: torch.Tensor, plane: torch.Tensor, block_table: torch.Tensor, positions: torch.Tensor,
@@ -1341,9 +1360,68 @@ def activation(x: torch.Tensor, out: torch.Tensor, kind: str):
                                   ACTIVATIONS[kind], _stream()), "activation")
 
 
+def glu(gu: torch.Tensor, out: torch.Tensor, kind: str):
+    """``out[t, i] = act(gu[t, i]) * gu[t, I + i]``: the hidden layer of a gated feed-forward whose gate and up
+    projections are one product (gate columns first).  ``kind``: ``silu`` or ``gelu_tanh``."""
+    _cuda(gu, out)
+    rows, I = out.shape
+    assert gu.shape == (rows, 2 * I) and gu.dtype == out.dtype and gu.stride(1) == 1 and out.stride(1) == 1
+    _check(lib().prism_glu(_ptr(gu), gu.stride(0), _ptr(out), out.stride(0), _dt(gu), rows, I, ACTIVATIONS[kind], _stream()),
+           "glu")
+
+
+def gather_gate(z: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, offset: int, out: torch.Tensor, kind: str,
+                err: torch.Tensor):
+    """``out[t, c] = act(z[t, c]) * table[ids[t], offset + c]``: a gate on a slice of a row gathered per token.
+    ``z [T, cols]`` float32, ``table [V, *]`` (float32 or bf16), ``out [T, cols]`` in the compute dtype."""
+    _cuda(z, ids, table, out)
+    T, cols = z.shape
+    assert z.dtype == torch.float32 and z.stride(1) == 1 and ids.dtype == torch.int32 and ids.shape[0] == T
+    assert table.dim() == 2 and table.stride(1) == 1 and 0 <= offset and offset + cols <= table.shape[1]
+    assert out.shape == (T, cols) and out.stride(1) == 1
+    _check(lib().prism_gather_gate(_ptr(z), z.stride(0), _ptr(ids), _ptr(table), _dt(table), table.stride(0), int(offset),
+                                   table.shape[0], _ptr(out), _dt(out), out.stride(0), T, cols, ACTIVATIONS[kind], _ptr(err),
+                                   _stream()), "gather_gate")
+
+
+def softcap(x: torch.Tensor, cap: float):
+    """``x <- cap * tanh(x / cap)`` in place on a contiguous float32 tensor."""
+    _cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _check(lib().prism_softcap(_ptr(x), x.numel(), float(cap), _stream()), "softcap")
+
+
+def add_rows(residual: torch.Tensor, delta: Optional[torch.Tensor], copy: Optional[torch.Tensor]):
+    """``residual += delta`` in place (float32 ``[T, H]``; ``delta`` None, ``[T, H]`` or a stack ``[k, T, H]`` of
+    partial sums) and ``copy`` (``[T, H]`` in the compute dtype, or None) receives the new rows: the residual sum
+    alone, for a sublayer that reads the stream itself."""
+    _cuda(residual, delta, copy)
+    assert residual.dtype == torch.float32 and residual.is_contiguous()
+    T, H = residual.shape
+    nsplit = 0
+    if delta is not None:
+        assert delta.is_contiguous() and delta.shape[-2:] == (T, H)
+        nsplit = 1 if delta.dim() == 2 else delta.shape[0]
+    if copy is not None:
+        assert copy.shape == (T, H) and copy.is_contiguous()
+    _check(lib().prism_add_rows(_ptr(residual), _ptr(delta), F32 if delta is None else _dt(delta), nsplit, T * H, _ptr(copy),
+                                F32 if copy is None else _dt(copy), T, H, _stream()), "add_rows")
+
+
+def feed_forward_glu(ctx, x: torch.Tensor, gate_up_w: torch.Tensor, down_w: torch.Tensor, kind: str):
+    """``down(act(gate(x)) * up(x))`` with the fused gate/up weight and ``act`` one of ``silu``, ``gelu_tanh``; silu
+    takes the path with the activation in the product's epilogue (``feed_forward_swiglu``)."""
+    if kind == "silu":
+        return feed_forward_swiglu(ctx, x, gate_up_w, down_w)
+    gu = linear(x, gate_up_w)
+    act = ctx.alloc((x.shape[0], gate_up_w.shape[0] // 2), x.dtype)
+    glu(gu, act, kind)
+    return linear_delta(act, down_w)
+
+
 def masked_attention(ctx, q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
                      block_table: torch.Tensor, num_pages: int, mask: KeyMask, scale: float,
-                     sink: Optional[torch.Tensor] = None):
+                     sink: Optional[torch.Tensor] = None, dist_bias: Optional[torch.Tensor] = None):
     """Attention of the step's tokens over one cache plane whose keys and values may differ in size, under a
     ``KeyMask`` and with an optional softmax sink.  The kernel is chosen by dtype and shape; the shape-generic
     one takes what the tensor-core kernel refuses."""
@@ -1354,10 +1432,10 @@ def masked_attention(ctx, q: torch.Tensor, out: torch.Tensor, k_plane: torch.Ten
         few = ctx.decode_only
         ns = masked_decode_splits(ctx.S, nkv * (-(-(nh // nkv) // 16)), mask.most_keys(ctx.max_kv_len)) if few else 1
         attention_masked_bf16(q, out, k_plane, v_plane, block_table, ctx.seg_start, ctx.cached_len, ctx.S,
-                              ctx.max_q_len, num_pages, mask, scale, sink, few, ctx.err, nsplit=ns)
+                              ctx.max_q_len, num_pages, mask, scale, sink, few, ctx.err, nsplit=ns, dist_bias=dist_bias)
         return
     attention_masked_generic(q, out, k_plane, v_plane, block_table, ctx.positions, ctx.tok_seg, num_pages, mask,
-                             scale, sink, ctx.err)
+                             scale, sink, ctx.err, dist_bias)
 
 
 MASKED_TC = os.environ.get("PRISM_MASKED_TC", "1") != "0"
@@ -1399,12 +1477,13 @@ def attention_masked_tc_ok(q, k_plane, v_plane, nh: int, nkv: int, dk: int, dv: 
 
 def attention_masked_bf16(q, out, k_plane, v_plane, block_table, seg_start, cached_len, S: int, max_q_len: int,
                           num_pages: int, mask: KeyMask, scale: float, sink: Optional[torch.Tensor], few_rows: bool,
-                          err: torch.Tensor, nsplit: int = 1):
+                          err: torch.Tensor, nsplit: int = 1, dist_bias: Optional[torch.Tensor] = None):
     """Tensor-core attention under a ``KeyMask`` with an optional sink; ``few_rows``: a decode step (one token
     per segment), where a CTA takes up to 16 query heads of a kv head, its four warps share the keys and
     ``nsplit`` CTAs the key tiles of one (segment, kv head), merged by a second kernel."""
-    _cuda(q, out, k_plane, v_plane, block_table, seg_start, cached_len, sink)
+    _cuda(q, out, k_plane, v_plane, block_table, seg_start, cached_len, sink, dist_bias)
     T, nh, dk = q.shape
+    _check_dist_bias(dist_bias, nh)
     P, nkv, dv = k_plane.shape[1], k_plane.shape[2], v_plane.shape[3]
     assert q.dtype == torch.bfloat16 and k_plane.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert q.stride(2) == 1 and out.stride(1) == 1 and out.shape == (T, nh * dv) and seg_start.shape[0] == S + 1
@@ -1420,7 +1499,8 @@ def attention_masked_bf16(q, out, k_plane, v_plane, block_table, seg_start, cach
         out.stride(0) if T > 1 else nh * dv, _ptr(k_plane), krs, khs, None if vin else _ptr(v_plane), vrs, vhs,
         _ptr(block_table), block_table.shape[1], _ptr(seg_start), _ptr(cached_len), S, int(max_q_len), nh, nkv, dk, dv,
         P, num_pages, mask.kind, mask.size, mask.keep, float(scale), _ptr(sink), F32 if sink is None else _dt(sink),
-        1 if few_rows else 0, int(nsplit) if few_rows else 1, _ptr(po), _ptr(pml), _ptr(err), _stream()),
+        1 if few_rows else 0, int(nsplit) if few_rows else 1, _ptr(po), _ptr(pml), _ptr(err), _ptr(dist_bias),
+        0 if dist_bias is None else dist_bias.shape[1] - 1, _stream()),
         "attention_masked_bf16")
     if few_rows and nsplit > 1:
         global launch_count
@@ -1630,21 +1710,23 @@ def headnorm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps
                                      {"silu": 0, "sigmoid": 1, "none": 2}[gate_act], _stream()), "headnorm_gate")
 
 
-SCAN_DELTA, SCAN_BONUS, SCAN_CHANNEL = 0, 1, 2      # csrc/recurrent.cu: PRISM_SCAN_*
+SCAN_DELTA, SCAN_BONUS, SCAN_CHANNEL, SCAN_GENERAL = 0, 1, 2, 3      # csrc/recurrent.cu: PRISM_SCAN_*
 
 
 def recurrent_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, ctx, H: int,
                    rep: int, dk: int, dv: int, out: torch.Tensor, bg: Optional[torch.Tensor] = None,
                    ww: Optional[torch.Tensor] = None, w0: Optional[torch.Tensor] = None, u: Optional[torch.Tensor] = None,
-                   decay_ready: bool = False):
+                   decay_ready: bool = False, ex: Optional[torch.Tensor] = None):
     """The step's tokens through a matrix-state recurrence, request by request, token after token, from and
     into ``state [slots, H, dv, dk]`` (float32).  ``q`` (or r), ``k``, ``v``: float32 rows ``[T, heads * size]`` with
     one row stride - column blocks of one product, or products of their own.  ``SCAN_DELTA``: delta rule with ``bg
     [T, 2 H]`` (beta | scalar decay), ``rep`` heads share a q/k head.  ``SCAN_BONUS``: per-channel decay ``exp(-exp(ww
     + w0))`` (``ww [T, H * dk]``) and bonus ``u [H * dk]`` for the current token; ``decay_ready``: ``ww`` holds the decay
     itself (``lowrank_decay``, ``decay_from_exponent``).  ``SCAN_CHANNEL``: delta rule whose decay is a vector over the
-    key channels, ``ww [T, H * dk]`` (the decay itself), with ``bg [T, H]`` (beta).  ``out [T, H, dv]`` float32."""
-    _cuda(q, k, v, state, out, bg, ww, w0, u)
+    key channels, ``ww [T, H * dk]`` (the decay itself), with ``bg [T, H]`` (beta).  ``SCAN_GENERAL``: the generalized
+    delta rule ``S <- diag(w) S - c (e^T S) + k v^T; o = S^T r`` with the decay ``ww [T, H * dk]`` and ``ex [T, 2 H dk]``
+    = unit key e | removal rate times e (``unit_removal``); every head has its own r and k.  ``out [T, H, dv]`` float32."""
+    _cuda(q, k, v, state, out, bg, ww, w0, u, ex)
     T = q.shape[0]
     for t in (q, k, v):
         assert t.dtype == torch.float32 and t.dim() == 2 and t.shape[0] == T and t.stride(1) == 1
@@ -1657,6 +1739,9 @@ def recurrent_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     elif mode == SCAN_CHANNEL:
         assert bg is not None and bg.shape == (T, H) and bg.is_contiguous() and bg.dtype == torch.float32
         assert ww.dtype == torch.float32 and ww.shape == (T, H * dk) and ww.stride(1) == 1
+    elif mode == SCAN_GENERAL:
+        assert rep == 1 and ww.dtype == torch.float32 and ww.shape == (T, H * dk) and ww.stride(1) == 1
+        assert ex is not None and ex.dtype == torch.float32 and ex.shape == (T, 2 * H * dk) and ex.is_contiguous()
     else:
         assert ww.dtype == torch.float32 and ww.shape == (T, H * dk) and ww.stride(1) == 1
         assert w0.numel() == H * dk and u.numel() == H * dk and w0.is_contiguous() and u.is_contiguous()
@@ -1667,19 +1752,35 @@ def recurrent_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
         int(mode), _ptr(q), stride, 0, k_off, v_off, _ptr(bg), _ptr(ww),
         0 if ww is None else ww.stride(0), _ptr(w0), F32 if w0 is None else _dt(w0), _ptr(u), F32 if u is None else _dt(u),
         _ptr(state), _ptr(ctx.seg_start), _ptr(ctx.state_slots), ctx.S, int(getattr(ctx, "max_q_len", None) or T), H, rep, dk, dv,
-        _ptr(out), 1 if decay_ready else 0, _stream()),
+        _ptr(out), 1 if decay_ready else 0, _ptr(ex), 0 if ex is None else ex.stride(0), _stream()),
         "recurrent_scan")
 
 
-LR_EXPEXP, LR_SOFTPLUS, LR_SIGMOID = 0, 1, 2      # csrc/recurrent.cu: PRISM_LR_*
+def unit_removal(k: torch.Tensor, a: torch.Tensor, a_bias: Optional[torch.Tensor], unit_eps: float, H: int, dk: int,
+                 ex: torch.Tensor):
+    """What the generalized delta rule takes out of its state, per token and head: ``ex[:, h dk + i] = e_i = k_i /
+    sqrt(sum k^2 + unit_eps)`` and ``ex[:, (H + h) dk + i] = sigmoid(a_i + a_bias_i) e_i``.  ``k``, ``a``: float32
+    column blocks ``[T, H * dk]`` of one product (one row stride); ``ex [T, 2 H dk]`` float32."""
+    _cuda(k, a, a_bias, ex)
+    T = k.shape[0]
+    assert k.dtype == a.dtype == torch.float32 and k.shape == a.shape == (T, H * dk) and k.stride(1) == a.stride(1) == 1
+    assert T == 1 or k.stride(0) == a.stride(0)
+    assert ex.dtype == torch.float32 and ex.shape == (T, 2 * H * dk) and ex.is_contiguous()
+    assert a_bias is None or (a_bias.numel() == H * dk and a_bias.is_contiguous())
+    _check(lib().prism_unit_removal(_ptr(k), _ptr(a), k.stride(0), _ptr(a_bias), F32 if a_bias is None else _dt(a_bias),
+                                    float(unit_eps), T, H, dk, _ptr(ex), _stream()), "unit_removal")
+
+
+LR_EXPEXP, LR_SOFTPLUS, LR_SIGMOID, LR_EXPSIG = 0, 1, 2, 3      # csrc/recurrent.cu: PRISM_LR_*
 
 
 def lowrank_decay(low: torch.Tensor, w2t: torch.Tensor, w0: Optional[torch.Tensor], out: torch.Tensor, inner_tanh: bool = True,
-                  epilogue: int = LR_EXPEXP, rate_log: Optional[torch.Tensor] = None, per: int = 1):
+                  epilogue: int = LR_EXPEXP, rate_log: Optional[torch.Tensor] = None, per: int = 1, rate: float = 1.0):
     """``out = epi(inner(low) @ w2t + w0)``: the second half of a low-rank product with what follows it, in one launch
     and in float32 throughout.  ``inner``: tanh or nothing.  ``epilogue``: ``LR_EXPEXP`` ``exp(-exp(z))`` (a per-channel
     decay from its double exponent), ``LR_SOFTPLUS`` ``exp(-exp(rate_log[n // per]) softplus(z))`` (a per-channel decay
-    with one rate per ``per`` channels), ``LR_SIGMOID`` (a gate).  ``low [T, R]`` float32 (row stride free), ``w2t [R,
+    with one rate per ``per`` channels), ``LR_SIGMOID`` (a gate), ``LR_EXPSIG`` ``exp(-rate sigmoid(z))`` (a per-channel
+    decay that stays above ``exp(-rate)``).  ``low [T, R]`` float32 (row stride free), ``w2t [R,
     N]`` float32 (the second matrix, transposed), ``w0 [N]`` or None, ``out [T, N]`` float32."""
     _cuda(low, w2t, w0, out, rate_log)
     T, R = low.shape
@@ -1691,7 +1792,7 @@ def lowrank_decay(low: torch.Tensor, w2t: torch.Tensor, w0: Optional[torch.Tenso
         assert rate_log is not None and rate_log.is_contiguous() and rate_log.numel() * per == N
     _check(lib().prism_lowrank_decay(_ptr(low), low.stride(0), R, _ptr(w2t), _ptr(w0), F32 if w0 is None else _dt(w0), N, T,
                                      _ptr(out), out.stride(0), 1 if inner_tanh else 0, int(epilogue), _ptr(rate_log),
-                                     F32 if rate_log is None else _dt(rate_log), int(per), _stream()), "lowrank_decay")
+                                     F32 if rate_log is None else _dt(rate_log), int(per), float(rate), _stream()), "lowrank_decay")
 
 
 def decay_from_exponent(ww: torch.Tensor, w0: torch.Tensor):
@@ -1738,21 +1839,22 @@ def hyper_norm(x: torch.Tensor, streams: int, x_out: Optional[torch.Tensor], del
 
 
 def causal_conv(x: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], tail: torch.Tensor, ctx, out: torch.Tensor,
-                move_tail: bool = False):
+                move_tail: bool = False, add_input: bool = False):
     """``out[t, c] = bias[c] + sum_j taps[c, K-1-j] x[t-j, c]``: a short causal convolution over time per channel,
     float32; ``x [T, C]`` (row stride free), ``taps [C, K]`` (last column: the current token's), ``tail [slots, K - 1,
     C]`` the request's last inputs before this step.  ``move_tail``: every request brings one token, and the kernel
-    moves the tail up itself (else ``state_tail`` follows)."""
+    moves the tail up itself (else ``state_tail`` follows).  ``add_input``: ``out = x + conv(x)``.  ``out``: float32
+    or the compute dtype (rounded once)."""
     _cuda(x, taps, bias, tail, out)
     T = x.shape[0]
     C, K = taps.shape
     assert x.dtype == torch.float32 and x.stride(1) == 1 and x.shape[1] == C and taps.is_contiguous()
     assert tail.dtype == torch.float32 and tail.is_contiguous() and tuple(tail.shape[1:]) == (max(K - 1, 0), C)
-    assert out.dtype == torch.float32 and out.shape == (T, C) and out.stride(1) == 1
+    assert out.shape == (T, C) and out.stride(1) == 1
     assert bias is None or (bias.shape == (C,) and bias.is_contiguous())
     _check(lib().prism_causal_conv(_ptr(x), x.stride(0), _ptr(taps), _dt(taps), _ptr(bias), F32 if bias is None else _dt(bias),
                                    K, C, _ptr(tail), _ptr(ctx.tok_seg), _ptr(ctx.seg_start), _ptr(ctx.state_slots), T, _ptr(out),
-                                   out.stride(0), 1 if move_tail else 0, _stream()), "causal_conv")
+                                   _dt(out), out.stride(0), 1 if move_tail else 0, 1 if add_input else 0, _stream()), "causal_conv")
 
 
 def block_gates(u: torch.Tensor, wr: torch.Tensor, wi: torch.Tensor, br: torch.Tensor, bi: torch.Tensor, lam: torch.Tensor,
@@ -1802,42 +1904,69 @@ def rglru_scan(a: torch.Tensor, g: torch.Tensor, y: torch.Tensor, state: torch.T
                                   _stream()), "rglru_scan")
 
 
-MOE_ACTS = {"silu": 0, "gelu_tanh": 1, "relu": 2}      # csrc/moe.cu: moe_act
+MOE_ACTS = {"silu": 0, "gelu_tanh": 1, "relu": 2, "relu2": 3}      # csrc/moe.cu: moe_act
 moe_tensor_cores = True                                 # bf16 experts on tcgen05 (csrc/moe_tcgen05.cu); False: CUDA cores
 
 
 MOE_ONE_CTA_TOKENS = 16       # steps of up to this many tokens are routed and placed by one CTA in one launch (a warp a token at a time: 64 tokens take longer than the three launches)
 
 
-def _moe_route_place(L, logits, T, E, top, softmax, renorm, pad, counts, offs, sel_e, sel_w, sel_rank, row_tok, row_w, row_dst):
+class MoeChoice:
+    """How a router's scores become a choice beyond "the largest": ``correction [E]`` is added to every score for
+    the choice only (the weights use the scores without it); the experts form ``groups`` equal groups of
+    neighbours, a group's score is its largest choice score, and only experts of the best ``keep`` groups can be
+    chosen; a choice's weight is divided by the sum of the chosen plus ``sum_eps`` (with renorm) and multiplied by
+    ``scale``."""
+
+    __slots__ = ("correction", "groups", "keep", "scale", "sum_eps")
+
+    def __init__(self, correction: Optional[torch.Tensor] = None, groups: int = 1, keep: int = 1, scale: float = 1.0,
+                 sum_eps: float = 0.0):
+        self.correction, self.groups, self.keep = correction, int(groups), int(keep)
+        self.scale, self.sum_eps = float(scale), float(sum_eps)
+
+
+def _moe_route_place(L, logits, T, E, top, softmax, renorm, pad, counts, offs, sel_e, sel_w, sel_rank, row_tok, row_w, row_dst,
+                     choice: Optional[MoeChoice] = None):
     sm, rn = 1 if softmax else 0, 1 if renorm else 0
-    if T <= MOE_ONE_CTA_TOKENS and 8 * E * 4 + (2 * E + 1) * 4 <= 48 * 1024:
+    ch = choice or MoeChoice()
+    corr = ch.correction
+    if corr is not None:
+        _cuda(corr)
+        assert corr.shape == (E,) and corr.is_contiguous()
+    assert ch.groups >= 1 and E % ch.groups == 0 and 1 <= ch.keep <= ch.groups and ch.keep * (E // ch.groups) >= top
+    extra = (_ptr(corr), F32 if corr is None else _dt(corr), ch.groups, ch.keep, ch.scale, ch.sum_eps)
+    if T <= MOE_ONE_CTA_TOKENS and 8 * (2 * E + 2 * ch.groups) * 4 + (2 * E + 1) * 4 <= 48 * 1024:
         _check(L.prism_moe_route_place(_ptr(logits), logits.stride(0), T, E, int(top), sm, rn, int(pad), _ptr(counts), _ptr(offs),
                                        _ptr(sel_e), _ptr(sel_w), _ptr(sel_rank), _ptr(row_tok), _ptr(row_w), _ptr(row_dst),
-                                       _stream()), "moe_route_place")
+                                       *extra, _stream()), "moe_route_place")
         return
     counts.zero_()
     _check(L.prism_moe_route(_ptr(logits), logits.stride(0), T, E, int(top), sm, rn, _ptr(counts), _ptr(sel_e), _ptr(sel_w),
-                             _ptr(sel_rank), _stream()), "moe_route")
+                             _ptr(sel_rank), *extra, _stream()), "moe_route")
     _check(L.prism_moe_place(_ptr(counts), _ptr(sel_e), _ptr(sel_w), _ptr(sel_rank), T, E, int(top), int(pad), _ptr(offs),
                              _ptr(row_tok), _ptr(row_w), _ptr(row_dst), _stream()), "moe_place")
 
 
 def moe_feed_forward(ctx, x: torch.Tensor, logits: torch.Tensor, gate_up_w: torch.Tensor, down_w: torch.Tensor, top: int,
-                     softmax: bool = False, renorm: bool = False, scale_input: bool = True, act: str = "silu") -> torch.Tensor:
+                     softmax: bool = False, renorm: bool = False, scale_input: bool = True, act: str = "silu",
+                     gated: bool = True, choice: Optional[MoeChoice] = None) -> torch.Tensor:
     """Mixture of experts on the step's rows: ``x [T, W]`` (compute dtype), router ``logits [T, E]`` float32,
     ``gate_up_w [E, 2 F, W]`` (an expert's gate rows, then its up rows), ``down_w [E, W, F]``.  Each token takes the
     ``top`` experts with the largest scores (sigmoid of the logits, or their softmax); a choice's weight is its score
     (``renorm``: over the sum of the chosen) and multiplies the expert's input (``scale_input``) or its output.
+    ``gated`` False: experts without a gate, ``down(act(up(a)))``, and ``gate_up_w`` is ``[E, F, W]``.  ``choice``: a
+    ``MoeChoice`` (correction, groups, weight scale).
     Returns float32 ``[top, T, W]``: one plane per choice, which the next norm adds up.  The rows are sorted by
     expert on the device and run as grouped products; the host never learns the counts.  bf16 with rows of 16-byte
     multiples: tcgen05 tiles of one expert each (``csrc/moe_tcgen05.cu``); otherwise CUDA cores (``csrc/moe.cu``)."""
     _cuda(x, logits, gate_up_w, down_w)
     T, W = x.shape
     E, F2, _ = gate_up_w.shape
-    F = F2 // 2
+    F = F2 // 2 if gated else F2
+    gt = 1 if gated else 0
     assert logits.dtype == torch.float32 and logits.shape == (T, E) and logits.stride(1) == 1 and x.stride(1) == 1
-    assert gate_up_w.shape == (E, 2 * F, W) and down_w.shape == (E, W, F) and gate_up_w.is_contiguous() and down_w.is_contiguous()
+    assert gate_up_w.shape == (E, (2 if gated else 1) * F, W) and down_w.shape == (E, W, F) and gate_up_w.is_contiguous() and down_w.is_contiguous()
     assert gate_up_w.dtype == x.dtype and down_w.dtype == x.dtype and 1 <= top <= E
     rows = T * top
     dev = x.device
@@ -1855,13 +1984,13 @@ def moe_feed_forward(ctx, x: torch.Tensor, logits: torch.Tensor, gate_up_w: torc
         flt = torch.empty(rows + padded, dtype=torch.float32, device=dev)
         sel_w, row_w = flt[:rows], flt[rows:]
         err = _tc_err_word(dev)
-        _moe_route_place(L, logits, T, E, top, softmax, renorm, ntok, counts, offs, sel_e, sel_w, sel_rank, None, None, None)
+        _moe_route_place(L, logits, T, E, top, softmax, renorm, ntok, counts, offs, sel_e, sel_w, sel_rank, None, None, None, choice)
         xs = ctx.alloc((padded, W), x.dtype)
         _check(L.prism_moe_gather(_ptr(x), x.stride(0), _ptr(offs), _ptr(sel_e), _ptr(sel_w), _ptr(sel_rank), T, int(top), W, si,
                                   _ptr(xs), _ptr(row_dst), _ptr(row_w), _stream()), "moe_gather")
         hidden = ctx.alloc((padded, F), x.dtype)
         _check(L.prism_moe_gemm_tcgen05(_ptr(xs), W, _ptr(gate_up_w), _ptr(offs), _ptr(counts), None, None, ntok, tiles, E, F, W,
-                                        1, MOE_ACTS[act], _ptr(hidden), F, _ptr(err), _stream()), "moe_gemm_tcgen05")
+                                        gt, MOE_ACTS[act], _ptr(hidden), F, _ptr(err), _stream()), "moe_gemm_tcgen05")
         y = ctx.alloc((top, T, W), torch.float32)
         _check(L.prism_moe_gemm_tcgen05(_ptr(hidden), F, _ptr(down_w), _ptr(offs), _ptr(counts), _ptr(row_dst),
                                         None if scale_input else _ptr(row_w), ntok, tiles, E, W, F, 0, 0, _ptr(y), W, _ptr(err),
@@ -1873,11 +2002,11 @@ def moe_feed_forward(ctx, x: torch.Tensor, logits: torch.Tensor, gate_up_w: torc
     sel_e, sel_rank, row_tok, row_dst = (ints[o + i * rows:o + (i + 1) * rows] for i in range(4))
     flt = torch.empty(2 * rows, dtype=torch.float32, device=dev)
     sel_w, row_w = flt[:rows], flt[rows:]
-    _moe_route_place(L, logits, T, E, top, softmax, renorm, 1, counts, offs, sel_e, sel_w, sel_rank, row_tok, row_w, row_dst)
+    _moe_route_place(L, logits, T, E, top, softmax, renorm, 1, counts, offs, sel_e, sel_w, sel_rank, row_tok, row_w, row_dst, choice)
     hidden = ctx.alloc((rows, F), x.dtype)
     _check(L.prism_moe_gemm(_ptr(x), x.stride(0), _ptr(gate_up_w), _dt(x), _ptr(offs), _ptr(row_tok), _ptr(row_w), _ptr(row_dst),
-                            rows, E, F, W, 1, si, MOE_ACTS[act], _ptr(hidden), F, _stream()), "moe_gemm")
+                            rows, E, F, W, 1, si, MOE_ACTS[act], _ptr(hidden), F, gt, _stream()), "moe_gemm")
     y = ctx.alloc((top, T, W), torch.float32)
     _check(L.prism_moe_gemm(_ptr(hidden), F, _ptr(down_w), _dt(x), _ptr(offs), _ptr(row_tok), _ptr(row_w), _ptr(row_dst),
-                            rows, E, W, F, 0, si, 0, _ptr(y), W, _stream()), "moe_gemm")
+                            rows, E, W, F, 0, si, 0, _ptr(y), W, 1, _stream()), "moe_gemm")
     return y

@@ -11,6 +11,7 @@ that is all the cache holds, next to one rotated key part shared by the heads.""
 
 from __future__ import annotations
 
+import math
 import warnings
 from typing import Optional
 
@@ -23,6 +24,25 @@ from .. import ops
 
 _warned = set()
 MAX_HEAD_DIM = 256        # the shape-generic attention kernel keeps one head's row in a warp's registers
+MAX_DISTANCE = 1 << 20    # the farthest distance a bias table by distance is laid out for (4 MB a head in float32)
+
+
+def distance_bucket(n: int, rows: int, far: int) -> int:
+    """The row of a distance-bias table with ``rows`` rows for the key ``n`` positions back: distances below ``rows //
+    2`` have a row each; the upper half is shared in logarithmic steps, ``half + floor(ln(n / half) / ln(far / half) *
+    (rows - half))``, and ends at ``far`` (every distance from there on has the last row).  The quotient of logarithms
+    is taken in float64 and a value within 1e-9 of a whole number counts as that number, so that distances at which
+    the formula is exact (n = half times a power of far / half with a whole exponent) land on their row."""
+    half = rows // 2
+    if n < half:
+        return n
+    if half == 0 or far <= half or n >= far:
+        return rows - 1
+    v = math.log(n / half) / math.log(far / half) * (rows - half)
+    if abs(v - round(v)) < 1e-9:
+        v = round(v)
+    return min(rows - 1, half + int(math.floor(v)))
+
 
 
 @register_part("mixer", "gqa_attention")
@@ -41,12 +61,16 @@ class GQAAttention(Mixer):
     multiplied by ``sigmoid(W_g h)`` before the output projection; ``gate="head"``: one gate number per head.
     ``sink_value``: a constant sink, the same for every head (0: one is added to the softmax's denominator).  ``out_scale``: a constant on the layer's result (folded into
     the gate).  A rotation with rescaled frequencies (``rotary_scaled``), the query/key norm and the gate
-    work from the float32 result of the input projection; so may a layer without keys and values of its own.  ``names``: the tensors' names in the model file (keys
+    work from the float32 result of the input projection; so may a layer without keys and values of its own.
+    ``qk_norm_weight`` False: the query/key norm has no weights (q and k are divided by their root mean square and
+    nothing else).  ``dist_bias``: a learned bias by distance on the scaled scores, ``dict(rows=B, far=D)``: a table
+    ``[B, heads]`` (tensor ``rel``) whose row for the key n positions back is ``distance_bucket(n, B, D)`` - one row
+    for each distance below ``B / 2``, the rest shared in steps that grow like a logarithm up to D.  ``names``: the tensors' names in the model file (keys
     q, k, v, o, q_b, k_b, v_b, o_b, sink, q_norm, k_norm, g)."""
 
     NAMES = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight",
                  q_b="q_proj.bias", k_b="k_proj.bias", v_b="v_proj.bias", o_b="o_proj.bias", sink="sinks",
-                 q_norm="q_norm.weight", k_norm="k_norm.weight", g="g_proj.weight")
+                 q_norm="q_norm.weight", k_norm="k_norm.weight", g="g_proj.weight", rel="rel")
     graph_safe = True
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
@@ -55,7 +79,7 @@ class GQAAttention(Mixer):
                  v_head_dim: Optional[int] = None, chunk: Optional[int] = None, sink: bool = False,
                  own_kv: bool = True, cache_chunk="mask", names: Optional[dict] = None, keep_first: int = 0,
                  qk_norm_eps: Optional[float] = None, gate=False, out_scale: float = 1.0, qk_norm_whole: bool = False,
-                 sink_value: Optional[float] = None):
+                 sink_value: Optional[float] = None, qk_norm_weight: bool = True, dist_bias: Optional[dict] = None):
         if num_heads % num_kv_heads:
             raise ConfigError(f"num_heads {num_heads} not divisible by num_kv_heads {num_kv_heads}")
         self.hidden_size, self.nh, self.nkv, self.hd = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
@@ -88,9 +112,17 @@ class GQAAttention(Mixer):
         # query/key norm, a rotation from a table of rescaled frequencies and the gate read the input projection's
         # float32 result
         self.float32_projection = self.qk_norm_eps is not None or self.gate or scaled
-        if self.float32_projection and qkv_bias:
-            raise ConfigError("query/key norm, rescaled rotation and output gate: for layers without biases on q, k, v")
-        self.general = (self.vhd != self.hd or self.chunk is not None or self.sink or not self.own_kv
+        if self.float32_projection and qkv_bias and self.gate:
+            raise ConfigError("an output gate beside biases on q, k, v is not built: the gate's rows have no bias")
+        self.qk_norm_weight = bool(qk_norm_weight)
+        self.dist_bias = None
+        if dist_bias is not None:
+            rows, far = int(dist_bias["rows"]), int(dist_bias["far"])
+            if rows < 1 or far < 1 or far > MAX_DISTANCE:
+                raise ConfigError(f"a distance bias needs at least one row and a farthest distance from 1 to {MAX_DISTANCE}, "
+                                  f"got rows {rows}, far {far}")
+            self.dist_bias = (rows, far)
+        self.general = (self.dist_bias is not None or self.vhd != self.hd or self.chunk is not None or self.sink or not self.own_kv
                         or self.sink_value is not None
                         or self.keep_first > 0 or self.float32_projection)
         self._own_in = self._own_out = True
@@ -147,7 +179,9 @@ class GQAAttention(Mixer):
                 ps.append(ParamSpec("qkv_b", b))
         if self.sink:
             ps.append(ParamSpec("sink", (WeightSource(self.names["sink"], (self.nh,), "bias"),)))
-        if self.qk_norm_eps is not None:
+        if self.dist_bias is not None:
+            ps.append(ParamSpec("rel", (WeightSource(self.names["rel"], (self.dist_bias[0], self.nh), "bias"),)))
+        if self.qk_norm_eps is not None and self.qk_norm_weight:
             nq, nk = (self.q_size, self.kv_size) if self.qk_norm_whole else (self.hd, self.hd)
             ps.append(ParamSpec("q_norm", (WeightSource(self.names["q_norm"], (nq,), "norm"),)))
             if self.own_kv:
@@ -189,6 +223,16 @@ class GQAAttention(Mixer):
         # other shape runs on the shape-generic kernel (one warp per token and head), correct but far slower.
         self.const_sink = (None if self.sink_value is None else
                            torch.full((self.nh,), self.sink_value, dtype=torch.float32, device=self.device))
+        self.bias_table = None
+        if self.dist_bias is not None and self.w.get("rel") is not None:
+            # the table by distance that the kernels index: [heads, far + 1], distances beyond `far` share the last entry
+            rows, far = self.dist_bias
+            idx = torch.tensor([distance_bucket(n, rows, far) for n in range(far + 1)], dtype=torch.long, device=self.device)
+            self.bias_table = self.w["rel"].float()[idx].t().contiguous()
+        self.plain_norm = None
+        if self.qk_norm_eps is not None and not self.qk_norm_weight:
+            n = max(self.q_size, self.kv_size) if self.qk_norm_whole else self.hd
+            self.plain_norm = torch.ones(n, dtype=torch.float32, device=self.device)
         if self.general:
             return
         if self.dtype == torch.bfloat16 and not ops.attention_bf16_shape_ok(self.hd, self.nh, self.nkv):
@@ -224,7 +268,7 @@ class GQAAttention(Mixer):
             ops.cache_store(qkv[:, qs:qs + kvs], cache.k, cache.block_table, ctx.positions, ctx.tok_seg, cache.num_pages,
                             ctx.max_positions, ctx.err, src2=qkv[:, qs + kvs:], plane2=cache.v)
         ops.masked_attention(ctx, q, out, cache.k, cache.v, cache.block_table, cache.num_pages, self.mask, self.scale,
-                             self._sink())
+                             self._sink(), self.bias_table)
 
     def _forward_inner_f32(self, ctx, x, cache, out, proj):
         """From the float32 projection ``[q | k | v | gate]`` (``[q | gate]`` in a layer without keys and values of
@@ -233,22 +277,27 @@ class GQAAttention(Mixer):
         T, qs = x.shape[0], self.q_size
         kvs, vs = (self.kv_size, self.v_size) if self.own_kv else (0, 0)
         if proj is None:
-            proj = ops.linear(x, self.w["qkv_w"], None, out_dtype=torch.float32)
+            proj = ops.linear(x, self.w["qkv_w"], self.w.get("qkv_b"), out_dtype=torch.float32)
         rot = self.position.rotary() if self.position is not None else None
         if self.position is not None and rot is None:
             raise ConfigError("with query/key norm or an output gate the attention part takes a rotary position encoding")
         q = ctx.alloc((T, self.nh, self.hd), ctx.dtype)
         own = self.own_kv
+        if self.plain_norm is not None:
+            wq = self.plain_norm[:self.q_size if self.qk_norm_whole else self.hd]
+            wk = self.plain_norm[:self.kv_size if self.qk_norm_whole else self.hd]
+        else:
+            wq, wk = self.w.get("q_norm"), self.w.get("k_norm")
         ops.qk_norm_rope_store(proj[:, :qs], proj[:, qs:qs + kvs] if own else None,
-                               proj[:, qs + kvs:qs + kvs + vs] if own else None, self.w.get("q_norm"),
-                               self.w.get("k_norm") if own else None, self.qk_norm_eps or 0.0,
+                               proj[:, qs + kvs:qs + kvs + vs] if own else None, wq,
+                               wk if own else None, self.qk_norm_eps or 0.0,
                                rot.inv_freq if rot and rot.rotary_dim else None, rot.rotary_dim if rot else 0, q,
                                cache.k if own else None, cache.v if own else None, cache.block_table, ctx.positions,
                                ctx.tok_seg, cache.num_pages, ctx.max_positions, ctx.err, whole=self.qk_norm_whole,
                                halves=bool(rot and not rot.interleaved), nkv=self.nkv)
         attn = ctx.alloc((T, self.nh * self.vhd), ctx.dtype) if self.gate else out
         ops.masked_attention(ctx, q, attn, cache.k, cache.v, cache.block_table, cache.num_pages, self.mask, self.scale,
-                             self._sink())
+                             self._sink(), self.bias_table)
         if self.gate:
             ops.gated_product(attn, proj[:, qs + kvs + vs:], out, "sigmoid", self.out_scale)
         elif self.out_scale != 1.0:

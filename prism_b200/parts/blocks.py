@@ -1,7 +1,9 @@
 """Arrangements of parts into a layer.  ``prenorm``: andre-fu/prism's decoder
 layer (engine/executor.py:106-127): norm, mixer, residual add, norm,
 feed-forward, residual add.  Each residual add is carried out by the norm
-that follows it (the next block's first norm, or the final norm).
+that follows it (the next block's first norm, or the final norm).  Options:
+a short causal convolution beside a skip path on what the mixer reads, no
+feed-forward, a per-layer token input after the feed-forward.
 ``parallel``: one norm whose output both the mixer and the feed-forward read;
 their two results are added to the residual stream together.
 ``postnorm``: the residual stream itself is normed after every sum,
@@ -13,23 +15,122 @@ from __future__ import annotations
 
 from typing import Optional
 
-from .base import Block, ParamSpec, PartSpec, StreamUpdate, WeightSource, build_part, register_part
+from .base import Block, CacheNeed, ParamSpec, PartSpec, StreamUpdate, WeightSource, build_part, register_part
 from .. import ops
 
 
 @register_part("block", "prenorm")
 class PreNormBlock(Block):
-    def __init__(self, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec, ff_norm: PartSpec):
+    """``x += mixer(norm(x)); x += feed_forward(norm(x))``, each sum carried out by the norm that follows it.
+
+    ``feed_forward`` None: the layer ends after its mixer.  ``input_conv`` K: what the mixer reads is ``h + conv(h)``
+    with h the normed rows and ``conv`` a causal convolution over time of K taps on each channel (tensor
+    ``conv_tensor`` ``[width, K]``, no bias, zeros before the sequence's start); the last ``K - 1`` normed rows of a
+    request are state of the layer, in a slot (float32), so a prompt may be cut anywhere.  h is formed and
+    convolved in float32 and rounded once.  ``token_side``: a per-layer token input after the feed-forward,
+
+        e = table[token][index * dim : (index + 1) * dim];   g = act(W_gate x) * e;   y = W_proj g
+        x <- x + y / sqrt(mean(y^2) + eps) * norm
+
+    with x the residual rows themselves (after the feed-forward's sum) and ``table`` the embedding's per-token side
+    table; arguments ``dim, index, eps, activation`` and ``names`` (keys gate, proj, norm)."""
+
+    SIDE_NAMES = dict(gate="side.gate", proj="side.proj", norm="side.norm")
+
+    def __init__(self, mixer: PartSpec, feed_forward: Optional[PartSpec], mixer_norm: PartSpec, ff_norm: Optional[PartSpec],
+                 hidden_size: Optional[int] = None, input_conv: Optional[int] = None, conv_tensor: str = "conv",
+                 token_side: Optional[dict] = None):
         self.mixer_norm = self.add_child("mixer_norm", build_part("norm", mixer_norm))
         self.mixer = self.add_child("mixer", build_part("mixer", mixer))
-        self.ff_norm = self.add_child("ff_norm", build_part("norm", ff_norm))
-        self.feed_forward = self.add_child("feed_forward", build_part("feed_forward", feed_forward))
+        self.ff_norm = self.add_child("ff_norm", build_part("norm", ff_norm)) if feed_forward is not None else None
+        self.feed_forward = (self.add_child("feed_forward", build_part("feed_forward", feed_forward))
+                             if feed_forward is not None else None)
+        if feed_forward is not None and ff_norm is None:
+            raise ValueError("a prenorm block with a feed-forward needs its norm")
+        self.taps = None if input_conv is None else int(input_conv)
+        self.conv_tensor = conv_tensor
+        self.side = None if token_side is None else dict(token_side)
+        if (self.taps is not None or self.side is not None) and hidden_size is None:
+            raise ValueError("an input convolution or a token input needs the block's hidden_size")
+        self.hidden_size = None if hidden_size is None else int(hidden_size)
+        if self.taps is not None and self.taps < 1:
+            raise ValueError(f"an input convolution needs at least one tap, got {input_conv}")
+        if self.side is not None:
+            self.side.setdefault("activation", "gelu_tanh")
+            self.side["names"] = dict(self.SIDE_NAMES, **(self.side.get("names") or {}))
+            if int(self.side["dim"]) < 1 or int(self.side["index"]) < 0:
+                raise ValueError("a token input needs a positive dim and the layer's index")
+
+    def cache_needs(self):
+        needs = tuple(self.mixer.cache_needs())
+        if self.taps is not None and self.taps > 1:
+            needs += (CacheNeed("state", state_shape=(self.taps - 1, self.hidden_size)),)
+        return needs
+
+    def cache_need(self):
+        needs = self.cache_needs()
+        return needs[0] if len(needs) == 1 else self.mixer.cache_need()
+
+    def params(self):
+        ps, W = [], self.hidden_size
+        if self.taps is not None:
+            ps.append(ParamSpec("conv_taps", (WeightSource(self.conv_tensor, (W, self.taps)),)))
+        if self.side is not None:
+            n, d = self.side["names"], int(self.side["dim"])
+            ps += [ParamSpec("side_gate", (WeightSource(n["gate"], (d, W)),)),
+                   ParamSpec("side_proj", (WeightSource(n["proj"], (W, d)),)),
+                   ParamSpec("side_norm", (WeightSource(n["norm"], (W,), "norm"),))]
+        return ps
+
+    def on_bound(self):
+        self.no_tail = None
+        if self.taps == 1:
+            self.no_tail = ops.torch.zeros((1, 0, self.hidden_size), dtype=ops.torch.float32, device=self.device)
+
+    def _mixer_input(self, ctx, residual, delta, cache):
+        """The normed rows the mixer reads (behind the input convolution, if the layer has one) and the mixer's own
+        part of the layer's cache views."""
+        if self.taps is None:
+            return self.mixer_norm.forward(ctx, residual, delta), cache
+        if self.taps > 1:
+            views = cache if isinstance(cache, tuple) else (cache,)
+            tail, rest = views[-1].state, views[:-1]
+            cache = None if not rest else (rest[0] if len(rest) == 1 else tuple(rest))
+        else:
+            tail = self.no_tail
+        h32 = self.mixer_norm.forward(ctx, residual, delta, out_dtype=ops.torch.float32)
+        h = ctx.alloc(tuple(h32.shape), ctx.dtype)
+        single = ctx.decode_only          # one token per request: the kernel that reads the tail also moves it up
+        ops.causal_conv(h32, self.w["conv_taps"], None, tail, ctx, h, move_tail=single, add_input=True)
+        if not single and self.taps > 1:
+            ops.state_tail(h32, tail, ctx)
+        return h, cache
+
+    def _token_side(self, ctx, residual, delta):
+        """Carries out the open sum, then the token input from the summed rows; returns the new open delta."""
+        table = ctx.scratch.get("token_side_table")
+        if table is None:
+            raise ValueError("a layer with a token input needs an embedding with a per-token side table")
+        d, i = int(self.side["dim"]), int(self.side["index"])
+        f32 = ctx.dtype == ops.torch.float32
+        xs = residual if f32 else ctx.alloc(tuple(residual.shape), ctx.dtype)
+        ops.add_rows(residual, delta, None if f32 else xs)
+        z = ops.linear(xs, self.w["side_gate"], None, out_dtype=ops.torch.float32)
+        g = ctx.alloc((residual.shape[0], d), ctx.dtype)
+        ops.gather_gate(z, ctx.token_ids, table, i * d, g, self.side["activation"], ctx.err)
+        y = ops.linear(g, self.w["side_proj"], None, out_dtype=ops.torch.float32)
+        out = ctx.alloc(tuple(y.shape), ops.torch.float32)
+        ops.rms_rows(y, self.w["side_norm"], float(self.side["eps"]), out)
+        return out
 
     def forward(self, ctx, residual, delta, cache):
-        h = self.mixer_norm.forward(ctx, residual, delta)
+        h, cache = self._mixer_input(ctx, residual, delta, cache)
         d = self.mixer.forward(ctx, h, cache)
-        h = self.ff_norm.forward(ctx, residual, d)
-        d = self.feed_forward.forward(ctx, h)
+        if self.feed_forward is not None:
+            h = self.ff_norm.forward(ctx, residual, d)
+            d = self.feed_forward.forward(ctx, h)
+        if self.side is not None:
+            d = self._token_side(ctx, residual, d)
         return residual, d
 
 

@@ -25,9 +25,11 @@ class RMSNorm(Norm):
     def params(self):
         return [ParamSpec("weight", (WeightSource(self.tensor, (self.width,), "norm"),), optional=self.optional)]
 
-    def forward(self, ctx, residual, delta, rows=None):
+    def forward(self, ctx, residual, delta, rows=None, out_dtype=None):
+        """``out_dtype``: the normed rows' dtype where it is not the compute dtype (float32 for a reader that goes on
+        in 32-bit)."""
         n = residual.shape[0] if rows is None else rows.shape[0]
-        out = ctx.alloc((n, self.width), ctx.dtype)
+        out = ctx.alloc((n, self.width), out_dtype or ctx.dtype)
         ops.add_rmsnorm(residual, delta, self.w["weight"], self.eps, out, rows)
         return out
 

@@ -11,6 +11,8 @@ short causal convolution over time of q, k and v.
 product, and a bonus for the current token in the read-out.
 ``channel_delta``: the delta rule with one decay per key channel, from a
 low-rank product, and a low-rank sigmoid gate on the read-out.
+``general_delta``: the generalized delta rule: a decay and a removal rate per
+key channel; what is removed is read along the unit key.
 ``rglru``: a recurrence with one number of state per channel whose gates are
 block-diagonal products, behind a short convolution, beside a gelu branch.
 ``sum``: several mixers side by side on the same input, their results scaled
@@ -209,6 +211,74 @@ class ChannelDeltaMixer(Mixer):
                            H, H // G, dk, dv, o, bg=beta, ww=ww)
         inner = ctx.alloc((T, H * dv), ctx.dtype)
         ops.headnorm_gate(o, gate, self.w["norm"], self.eps, self.out_scale, inner, gate_act="none")
+        return ops.linear_delta(inner, self.w["o_w"], None, f32=True)
+
+
+@register_part("mixer", "general_delta")
+class GeneralDeltaMixer(Mixer):
+    """The generalized delta rule: a decay and a removal rate of their own for every key channel.  With h the input,
+    per token and head (``num_heads`` heads of ``head_dim`` key and value channels)::
+
+        r, k, v = W_r h, W_k h, W_v h
+        w = exp(-decay_rate sigmoid(W_w2 tanh(W_w1 h) + w0))            per key channel: a decay in (exp(-decay_rate), 1)
+        a = sigmoid(W_a h + a_b)                                        per key channel: a removal rate
+        e = k / sqrt(sum k^2 + unit_eps)                                the unit key
+        S <- diag(w) S - (a * e) (e^T S) + k v^T;   o = S^T r           both corrections read the state before the token
+        out = W_o [o / rms(o) * norm * sigmoid(W_g h)]
+
+    State per request: S ``[H, head_dim, head_dim]`` (stored column by column), float32, starting at zero.  All input
+    projections are one product with float32 results; the decay's second, rank-sized product runs in float32 with
+    its epilogue in the same launch; unit key, removal, state, head norm and gate are float32.  The decay's rank
+    is the shape of ``w1``.  ``names``: keys r, k, v, g, a, a_b, w1, w2, w0, norm, o."""
+
+    NAMES = dict(r="r", k="k", v="v", g="g", a="a", a_b="a.b", w1="w1", w2="w2", w0="w0", norm="norm", o="o")
+    graph_safe = True
+    float32_projection = True
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, decay_rank: int, eps: float, decay_rate: float,
+                 unit_eps: float = 1e-6, out_scale: float = 1.0, names: Optional[dict] = None):
+        self.hidden_size, self.H, self.d, self.rank = int(hidden_size), int(num_heads), int(head_dim), int(decay_rank)
+        if min(self.H, self.d, self.rank) < 1 or self.d > 1024:
+            raise ConfigError("general delta mixer: heads, head size and the decay's rank must be positive, the head size "
+                              "at most 1024")
+        self.eps, self.unit_eps, self.out_scale = float(eps), float(unit_eps), float(out_scale)
+        self.decay_rate = float(decay_rate)
+        self.names = dict(self.NAMES, **(names or {}))
+
+    def cache_needs(self):
+        return (CacheNeed("state", state_shape=(self.H, self.d, self.d)),)
+
+    def cache_need(self):
+        return self.cache_needs()[0]
+
+    def params(self):
+        W, n, A, R = self.hidden_size, self.names, self.H * self.d, self.rank
+        return [ParamSpec("in_w", tuple(WeightSource(n[s], (A, W)) for s in "rkvga") + (WeightSource(n["w1"], (R, W)),)),
+                ParamSpec("a_b", (WeightSource(n["a_b"], (A,), "bias"),)),
+                ParamSpec("w2", (WeightSource(n["w2"], (A, R)),)),
+                ParamSpec("w0", (WeightSource(n["w0"], (A,), "bias"),)),
+                ParamSpec("norm", (WeightSource(n["norm"], (A,), "norm"),)),
+                ParamSpec("o_w", (WeightSource(n["o"], (W, A)),))]
+
+    def on_bound(self):
+        # the decay's second product runs in float32 whatever the engine's dtype (its input is the float32 tanh);
+        # transposed, so that the kernel's neighbouring threads read neighbouring floats
+        self.w2t = self.w["w2"].float().t().contiguous() if self.w["w2"] is not None else None
+
+    def forward(self, ctx, x, cache):
+        state = cache[0] if isinstance(cache, tuple) else cache
+        T, H, d, A = x.shape[0], self.H, self.d, self.H * self.d
+        proj = ops.linear(x, self.w["in_w"], None, out_dtype=torch.float32)          # r | k | v | g | a | w1
+        r, k, v, g, a = (proj[:, i * A:(i + 1) * A] for i in range(5))
+        low = proj[:, 5 * A:]
+        ww = ctx.alloc((T, A), torch.float32)
+        ops.lowrank_decay(low, self.w2t, self.w["w0"], ww, epilogue=ops.LR_EXPSIG, rate=self.decay_rate)
+        ex = ctx.alloc((T, 2 * A), torch.float32)
+        ops.unit_removal(k, a, self.w["a_b"], self.unit_eps, H, d, ex)
+        o = ctx.alloc((T, H, d), torch.float32)
+        ops.recurrent_scan(ops.SCAN_GENERAL, r, k, v, state.state, ctx, H, 1, d, d, o, ww=ww, ex=ex)
+        inner = ctx.alloc((T, A), ctx.dtype)
+        ops.headnorm_gate(o, g, self.w["norm"], self.eps, self.out_scale, inner, gate_act="sigmoid")
         return ops.linear_delta(inner, self.w["o_w"], None, f32=True)
 
 
