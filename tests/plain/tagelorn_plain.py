@@ -78,6 +78,8 @@ def distance_bucket(n: int, rows: int, far: int) -> int:
     half = rows // 2
     if n < half:
         return n
+    if half == 0 or far <= half:
+        return rows - 1
     v = math.log(n / half) / math.log(far / half) * (rows - half)
     if abs(v - round(v)) < 1e-9:
         v = round(v)
@@ -92,8 +94,9 @@ def attention(h, w, p, mx, eps, rnd=_same):
     """Grouped-query attention: biases, q and k divided by their root mean square per head, a bias by distance, a window
     that keeps the first positions, a sink in the softmax's denominator."""
     T = h.shape[0]
-    H, G, d, dv = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
-    size, keep = mx["mask"]["size"], mx["mask"]["keep_first"]
+    H, G, d = mx["heads"], mx.get("kv_heads") or mx["heads"], mx["dim"]
+    dv = mx.get("vdim") or d
+    size, keep = mx["mask"]["size"], mx["mask"].get("keep_first", 0)
     q = (h @ w[p + "q"].T + w[p + "q.b"]).view(T, H, d)
     k = (h @ w[p + "k"].T + w[p + "k.b"]).view(T, G, d)
     v = (h @ w[p + "v"].T + w[p + "v.b"]).view(T, G, dv)
@@ -161,13 +164,15 @@ def route(z, correction, top, groups, keep, scale):
     return chosen, [s[e] / wsum * scale for e in chosen]
 
 
-def moe_ff(h, w, p, mlp, rnd=_same, route_dtype=None):
+def moe_ff(h, w, p, mlp, rnd=_same):
     T = h.shape[0]
     rt = mlp["router"]
     z = h @ w[p + "router"].T
     out = torch.zeros(T, w[p + "e0.down"].shape[0], dtype=h.dtype)
     for t in range(T):
-        chosen, weights = route(z[t], w[p + "correction"], rt["top"], rt["groups"]["count"], rt["groups"]["keep"], rt["scale"])
+        groups = rt.get("groups") or {}
+        count = groups.get("count", 1)
+        chosen, weights = route(z[t], w[p + "correction"], rt["top"], count, groups.get("keep", count), rt.get("scale", 1.0))
         for e, ww in zip(chosen, weights):
             out[t] += ww * expert(h[t:t + 1], w, f"{p}e{e}.", rnd)[0]
     if mlp.get("shared"):
@@ -191,7 +196,7 @@ def forward(cfg, w, tokens, rnd=_same, streams=None):
     """Logits ``[T, vocab]`` for one sequence.  ``streams``: a list that receives the residual rows after every layer."""
     eps = cfg["norm"]["eps"]
     tokens = torch.as_tensor(tokens, dtype=torch.long)
-    x = embed(tokens, w["embed"], cfg["embedding"]["scale"])
+    x = embed(tokens, w["embed"], (cfg.get("embedding") or {}).get("scale", 1.0))
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
         h = rms(x, eps) * w[p + "norm1"]
