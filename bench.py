@@ -492,7 +492,7 @@ def main():
     ap.add_argument("--model", default="7b", choices=sorted(SHAPES), help="layer sizes (default: the headline's)")
     ap.add_argument("--prompt-len", type=int, default=2048, help="prompt tokens (context = twice as many)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
-    ap.add_argument("--design", default=None, choices=["dolezen", "pofazen", "zuvulorn"],
+    ap.add_argument("--design", default=None, choices=["dolezen", "pofazen", "zuvulorn", "tagelorn"],
                     help="instead of the headline: prefill and decode throughput of this design beside Qwen2 at equal "
                          "size, with the attention kernels of both (benchmarks/design_bench.py)")
     ap.add_argument("--sizes", default="2k,4k", help="with --design: the layer sizes to measure")

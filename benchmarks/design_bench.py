@@ -1,8 +1,9 @@
-"""Prefill and decode throughput of the Dolezen, the Pofazen or the Zuvulorn design at layer sizes that resemble real models
-(random weights, bf16), beside the Qwen2 architecture at equal width, depth and parameter count, and the
-design's own kernels beside Qwen2's on the same problem with their fractions of the measured peaks.
+"""Prefill and decode throughput of the Dolezen, the Pofazen, the Zuvulorn or the Tagelorn design at layer sizes that resemble real models
+(random weights, bf16), beside the Qwen2 architecture at equal width, depth and parameter count (Tagelorn also beside
+Zuvulorn, the closest of the other designs: attention with a sink, a delta rule with a decay per key channel, experts), and the
+design's own kernels beside the like kernels on the same problem with their fractions of the measured peaks.
 
-    python bench.py --design dolezen|pofazen|zuvulorn [--sizes 2k,4k] [--steps K] [--warmup W]
+    python bench.py --design dolezen|pofazen|zuvulorn|tagelorn [--sizes 2k,4k] [--steps K] [--warmup W]
     python benchmarks/design_bench.py [--design pofazen] [--sizes 2k] [--kernels-only] [--once KERNEL]
 
 One JSON line.  Timing: CUDA events after W >= 3 warm-up runs; every timed step reads all weights (more than
@@ -476,8 +477,151 @@ def zuvulorn_kernel_numbers(s, pk, once=None):
     return out
 
 
+TAGELORN_BIAS_ROWS, TAGELORN_BIAS_FAR, TAGELORN_SIDE = 32, 2048, 64
+
+
+def tagelorn_ff(s):
+    """Inner width of a Tagelorn expert (two matrices each): eight routed experts and the shared one together weigh what
+    Qwen2's gated feed-forward of three matrices does."""
+    return s["ff"] * 2 // 3 // 256 * 256 * 3 // 2 // (MOE_EXPERTS + 1) // 32 * 32
+
+
+def tagelorn_config(s):
+    """Layers: windowed attention (keeps the first four positions, bias by distance, sink), generalized delta rule, ...;
+    every layer behind an input convolution of four taps and followed by a token input; the first layer's feed-forward
+    dense, the others 8 experts in 4 groups (2 groups kept, 2 experts a token) and a shared one."""
+    att = dict(heads=s["heads"], kv_heads=s["kv_heads"], dim=s["dim"], vdim=s["vdim"], scale=s["dim"] ** -0.5,
+               mask=dict(size=s["window"], keep_first=4), bias_max=TAGELORN_BIAS_FAR, bias_rows=TAGELORN_BIAS_ROWS)
+    gd = dict(heads=s["heads"], dim=s["dim"], decay_rank=64)
+    F = tagelorn_ff(s)
+    routed = dict(kind="moe", expert=dict(ff=F), shared=dict(ff=F),
+                  router=dict(experts=MOE_EXPERTS, top=MOE_TOP, scale=2.5, groups=dict(count=4, keep=2)))
+    layers = []
+    for i in range(s["layers"]):
+        mlp = dict(kind="dense", ff=s["ff"] * 2 // 3 // 256 * 256) if i == 0 else routed
+        layers.append(dict(type="attention" if i % 2 == 0 else "general_delta", mixer=dict(att if i % 2 == 0 else gd), mlp=mlp))
+    return dict(architecture="Tagelorn", vocab=s["vocab"], width=s["width"], norm=dict(eps=1e-6), canon=dict(taps=4),
+                embedding=dict(scale=1.0), token_side=dict(dim=TAGELORN_SIDE), logit_softcap=30.0, layers=layers,
+                max_positions=8192)
+
+
+def tagelorn_kernel_numbers(s, pk, once=None):
+    """The design's kernels alone, each beside the like kernel of the closest model on the same problem: attention
+    under a window with kept positions, a sink and the bias by distance beside the same kernel without the bias (and
+    Qwen2's kernels under the window); the generalized delta rule beside the delta rule with a decay per key channel;
+    the experts without a gate, routed by groups, beside gated experts of the same total weight; the input
+    convolution beside the skip path, the sinusoid embedding, and the token input's small kernels by their bytes."""
+    from prism_b200 import ops
+    from prism_b200.parts.attention import distance_bucket
+    out = {}
+    T = 2048
+    nh, nkv, dk, dv, W, win = s["heads"], s["kv_heads"], s["dim"], s["vdim"], s["width"], s["window"]
+    shapes = (("prefill_2048", 1, 0, T), ("decode_b8", 8, T - 1, 1), ("decode_b64", 64, T - 1, 1))
+    mask = ops.KeyMask.window(win, 4)
+
+    def run(name, fn, flops, nbytes, fp32=False):
+        if once:
+            if once == name:
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize()
+            return
+        ms = timeit(fn)
+        if fp32:
+            out[name] = dict(us=round(ms * 1e3, 1), fp32_tflops=round(flops / ms / 1e9, 2), gbs=round(nbytes / ms / 1e6, 1),
+                             frac_hbm_of_measured=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4))
+        else:
+            out[name] = _rates(ms, flops, nbytes, pk)
+
+    sink = torch.randn(nh, device=DEV)
+    rel = torch.randn(TAGELORN_BIAS_ROWS, nh)
+    idx = torch.tensor([distance_bucket(n, TAGELORN_BIAS_ROWS, TAGELORN_BIAS_FAR) for n in range(TAGELORN_BIAS_FAR + 1)])
+    table = rel[idx].t().contiguous().to(DEV)
+    for label, batch, cached, q_len in shapes:
+        c, kc, vc, bt, npages = paged(batch, cached, q_len, nkv, dk, dv)
+        q = torch.randn(batch * q_len, nh, dk, device=DEV, dtype=torch.bfloat16)
+        o = torch.empty(batch * q_len, nh * dv, device=DEV, dtype=torch.bfloat16)
+        pairs = batch * sum(min(p + 1, win) + min(4, max(0, p + 1 - win)) for p in range(cached, cached + q_len))
+        keys = batch * (min(cached + q_len, win + 4) if q_len == 1 else cached + q_len)
+        flops, nbytes = 2 * pairs * nh * (dk + dv), 2 * (keys * nkv * (dk + dv) + batch * q_len * nh * (dk + dv))
+        run(f"biased_window_{label}", lambda: ops.masked_attention(c, q, o, kc, vc, bt, npages, mask, dk ** -0.5, sink, table), flops, nbytes)
+        run(f"like_window_sink_{label}", lambda: ops.masked_attention(c, q, o, kc, vc, bt, npages, mask, dk ** -0.5, sink), flops, nbytes)
+        if q_len == 1:
+            ns = ops.decode_splits(batch, nkv, cached + 1, win)
+            po = torch.empty(batch, nh, ns, dk, device=DEV)
+            pml = torch.empty(batch, nh, ns, 2, device=DEV)
+            run(f"qwen2_window_{label}", lambda: ops.attention_decode_bf16(q, o, kc, vc, bt, c.positions, c.tok_seg, npages, win,
+                                                                           dk ** -0.5, ns, po, pml, c.err), flops, nbytes)
+        else:
+            run(f"qwen2_window_tcgen05_{label}", lambda: ops.attention_prefill_tc(q, o, kc, vc, bt, c.seg_start, c.cached_len, q_len,
+                                                                                  npages, win, dk ** -0.5, c.err), flops, nbytes)
+            run(f"qwen2_window_mma_sync_{label}", lambda: ops.attention_prefill_bf16(q, o, kc, vc, bt, c.seg_start, c.cached_len,
+                                                                                     q_len, npages, win, dk ** -0.5, c.err), flops, nbytes)
+    # the matrix-state scans: decay and removal per key channel (this design) beside a decay per key channel (the like kernel)
+    H = nh
+    for label, batch, cached, q_len in shapes:
+        Tt = batch * q_len
+        c = types.SimpleNamespace(seg_start=(torch.arange(batch + 1, dtype=torch.int32) * q_len).to(DEV),
+                                  state_slots=torch.arange(batch, dtype=torch.int32, device=DEV), S=batch, max_q_len=q_len)
+        state = torch.zeros(batch + 1, H, dv, dk, device=DEV)
+        o = torch.empty(Tt, H, dv, device=DEV)
+        x = torch.nn.functional.normalize(torch.randn(Tt, 3 * H, dk, device=DEV), dim=-1).view(Tt, -1)
+        ww = torch.rand(Tt, H * dk, device=DEV) * 0.4 + 0.6
+        ex = torch.cat([x[:, H * dk:2 * H * dk], x[:, H * dk:2 * H * dk] * 0.5], 1).contiguous()
+        beta = torch.rand(Tt, H, device=DEV)
+        flops = 6 * Tt * H * dk * dv
+        run(f"general_scan_{label}", lambda: ops.recurrent_scan(ops.SCAN_GENERAL, x[:, :H * dk], x[:, H * dk:2 * H * dk], x[:, 2 * H * dk:],
+                                                                state, c, H, 1, dk, dv, o, ww=ww, ex=ex), flops,
+            4 * (2 * batch * H * dk * dv + Tt * H * (5 * dk + 2 * dv)), fp32=True)
+        run(f"like_channel_scan_{label}", lambda: ops.recurrent_scan(ops.SCAN_CHANNEL, x[:, :H * dk], x[:, H * dk:2 * H * dk], x[:, 2 * H * dk:],
+                                                                     state, c, H, 1, dk, dv, o, bg=beta, ww=ww), flops,
+            4 * (2 * batch * H * dk * dv + Tt * H * (3 * dk + 2 * dv)), fp32=True)
+    # experts without a gate, routed by groups, beside gated experts of the same total weight (the like kernels) and the dense layer
+    E, top, F, Fz = MOE_EXPERTS, MOE_TOP, tagelorn_ff(s) * (MOE_EXPERTS + 1) // MOE_EXPERTS // 32 * 32, moe_ff(s)
+    Fd = s["ff"] * 2 // 3 // 256 * 256
+    up = torch.randn(E, F, W, device=DEV, dtype=torch.bfloat16) / W ** 0.5
+    dn = torch.randn(E, W, F, device=DEV, dtype=torch.bfloat16) / F ** 0.5
+    guz = torch.randn(E, 2 * Fz, W, device=DEV, dtype=torch.bfloat16) / W ** 0.5
+    dnz = torch.randn(E, W, Fz, device=DEV, dtype=torch.bfloat16) / Fz ** 0.5
+    gud = torch.randn(2 * Fd, W, device=DEV, dtype=torch.bfloat16) / W ** 0.5
+    dnd = torch.randn(W, Fd, device=DEV, dtype=torch.bfloat16) / Fd ** 0.5
+    actx = types.SimpleNamespace(alloc=lambda shape, dtype: torch.empty(shape, dtype=dtype, device=DEV))
+    choice = ops.MoeChoice(torch.randn(E, device=DEV) * 0.05, 4, 2, 2.5, 1e-20)
+    for label, Tt in (("prefill_2048", T), ("decode_b8", 8), ("decode_b64", 64)):
+        xx = torch.randn(Tt, W, device=DEV, dtype=torch.bfloat16)
+        logits = torch.randn(Tt, E, device=DEV)
+        used = min(E, Tt * top)
+        run(f"grouped_experts_{label}", lambda: ops.moe_feed_forward(actx, xx, logits, up, dn, top, True, True, False, "relu2", False, choice),
+            4 * Tt * top * F * W, 2 * (2 * used * F * W + Tt * W * (1 + 2 * top)))
+        run(f"like_gated_experts_{label}", lambda: ops.moe_feed_forward(actx, xx, logits, guz, dnz, top), 6 * Tt * top * Fz * W,
+            2 * (3 * used * Fz * W + Tt * W * (1 + 2 * top)))
+        run(f"gelu_feed_forward_{label}", lambda: ops.feed_forward_glu(actx, xx, gud, dnd, "gelu_tanh"), 6 * Tt * Fd * W,
+            2 * (3 * Fd * W + 3 * Tt * W))
+        run(f"qwen2_feed_forward_{label}", lambda: ops.feed_forward_swiglu(actx, xx, gud, dnd), 6 * Tt * Fd * W,
+            2 * (3 * Fd * W + 3 * Tt * W))
+    # the input convolution beside the skip path (float32 normed rows in, compute dtype out), beside add + norm on the same rows
+    taps = torch.randn(W, 4, device=DEV, dtype=torch.bfloat16)
+    wn = torch.ones(W, device=DEV)
+    for label, batch, q_len in (("prefill_2048", 1, T), ("decode_b64", 64, 1)):
+        Tt = batch * q_len
+        c = types.SimpleNamespace(seg_start=(torch.arange(batch + 1, dtype=torch.int32) * q_len).to(DEV),
+                                  tok_seg=torch.arange(batch, dtype=torch.int32).repeat_interleave(q_len).to(DEV),
+                                  state_slots=torch.arange(batch, dtype=torch.int32, device=DEV), S=batch, max_q_len=q_len)
+        h32 = torch.randn(Tt, W, device=DEV)
+        tail = torch.zeros(batch + 1, 3, W, device=DEV)
+        h = torch.empty(Tt, W, device=DEV, dtype=torch.bfloat16)
+        run(f"input_conv_{label}", lambda: ops.causal_conv(h32, taps, None, tail, c, h, move_tail=q_len == 1, add_input=True), 0,
+            4 * Tt * W + 2 * Tt * W + (8 * 3 * batch * W if q_len == 1 else 0), fp32=True)
+        d = torch.randn(Tt, W, device=DEV)
+        x1 = torch.randn(Tt, W, device=DEV)
+        run(f"qwen2_add_norm_{label}", lambda: ops.add_rmsnorm(x1, d, wn, 1e-6, h), 0, 4 * Tt * W * 3 + 2 * Tt * W, fp32=True)
+    return out
+
+
 DESIGNS = {"dolezen": (dolezen_config, kernel_numbers), "pofazen": (pofazen_config, pofazen_kernel_numbers),
-           "zuvulorn": (zuvulorn_config, zuvulorn_kernel_numbers)}
+           "zuvulorn": (zuvulorn_config, zuvulorn_kernel_numbers), "tagelorn": (tagelorn_config, tagelorn_kernel_numbers)}
+# designs measured beside another design as well as beside Qwen2: the closest of the models that ran before
+BESIDE = {"tagelorn": ("zuvulorn", zuvulorn_config)}
 
 
 def run(sizes, steps, warmup, prompt_len=2048, batch=8, kernels_only=False, once=None, peaks=None, design="dolezen"):
@@ -491,9 +635,17 @@ def run(sizes, steps, warmup, prompt_len=2048, batch=8, kernels_only=False, once
         s = SIZES[name]
         entry = dict(shape=s)
         if not kernels_only and not once:
-            for label, raw in ((design, make_config(s)), ("qwen2", qwen2_config(s))):
+            models = [(design, make_config(s)), ("qwen2", qwen2_config(s))]
+            if design in BESIDE:
+                models.append((BESIDE[design][0], BESIDE[design][1](s)))
+            for label, raw in models:
                 entry[label] = engine_numbers(raw, prompt_len, batch, steps, warmup)
                 launches += entry[label].pop("launches")
+            if design in BESIDE:
+                other = BESIDE[design][0]
+                entry[f"{design}_over_{other}"] = dict(
+                    prefill=round(entry[design]["prefill_tokens_per_s"] / entry[other]["prefill_tokens_per_s"], 3),
+                    decode=round(entry[design]["decode_tokens_per_s"] / entry[other]["decode_tokens_per_s"], 3))
             entry[f"{design}_over_qwen2"] = dict(
                 prefill=round(entry[design]["prefill_tokens_per_s"] / entry["qwen2"]["prefill_tokens_per_s"], 3),
                 decode=round(entry[design]["decode_tokens_per_s"] / entry["qwen2"]["decode_tokens_per_s"], 3))

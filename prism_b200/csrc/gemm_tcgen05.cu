@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(THREADS)
 gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                  const void* __restrict__ bias, int bias_bf16, void* __restrict__ y, int ldy, int M, int N, int K,
                  int kblocks_per_split, int pair_offset, float* __restrict__ ws, int* __restrict__ counters, int* err,
-                 int group_rows, int group_tokens) {
+                 int group_rows, int group_tokens, int glu_act) {
     using C = Cfg<NTOK, EPI>;
     constexpr int W_TILES = C::W_TILES;
     constexpr int STAGES = C::STAGES;
@@ -212,7 +212,9 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                     if (n >= M) continue;
                     if (EPI == EPI_SWIGLU) {
                         const float g = acc[0][n], u = acc[W_TILES - 1][n];
-                        reinterpret_cast<__nv_bfloat16*>(y)[(size_t)n * ldy + m] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+                        const float a = glu_act ? 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)))
+                                                : g / (1.f + expf(-g));
+                        reinterpret_cast<__nv_bfloat16*>(y)[(size_t)n * ldy + m] = __float2bfloat16_rn(a * u);
                     } else if (EPI == EPI_PARTIAL) {
                         reinterpret_cast<float*>(y)[((size_t)blockIdx.y * M + n) * ldy + m] = acc[0][n];
                     } else if (EPI == EPI_F32) {
@@ -238,7 +240,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 template <int NTOK, int EPI>
 int launch(const void* W, int ldw, long long w_rows, const void* x, int ldx, const void* bias, int bias_bf16, void* y,
            int ldy, int M, int N, int K, int ksplit, int pair_offset, float* ws, int* counters, int* err,
-           int group_rows, int group_tokens, cudaStream_t stream) {
+           int group_rows, int group_tokens, int glu_act, cudaStream_t stream) {
     using C = Cfg<NTOK, EPI>;
     CUtensorMap mw, mx;
     int rc = make_map(&mw, W, w_rows, K, ldw, TILE_M);
@@ -252,7 +254,7 @@ int launch(const void* W, int ldw, long long w_rows, const void* x, int ldx, con
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
     dim3 grid((N + TILE_M - 1) / TILE_M, ksplit);
     return (int)launch_kernel(kern, grid, dim3(THREADS), C::SMEM, stream, mw, mx, bias, bias_bf16, y, ldy, M, N, K, per,
-                              pair_offset, ws, counters, err, group_rows, group_tokens);
+                              pair_offset, ws, counters, err, group_rows, group_tokens, glu_act);
 }
 
 }  // namespace tc
@@ -270,7 +272,7 @@ PRISM_EXPORT int prism_gemm_tcgen05_supported(int M, int N, int K) {
 }
 
 // epi: 0 bf16 (+bias), 1 float32 (+bias), 2 paired SwiGLU (W is [2N, K]; bf16 out [M, N]),
-// 3 partial sums: y is float32 [ksplit, M, N] (ldy = N), no bias.
+// 3 partial sums: y is float32 [ksplit, M, N] (ldy = N), no bias; 4: as 2 with the gate through gelu_tanh instead of silu.
 // ksplit > 1 with epi 0 or 1 needs a workspace `ws` of ksplit * M * N floats and `counters`, one int per
 // 128-row tile of N, zero before the first launch (the kernel leaves them zero); the last CTA of each
 // tile adds the partial sums in split order, so the result does not depend on timing.  Not with epi 2.
@@ -281,6 +283,8 @@ PRISM_EXPORT int prism_gemm_tcgen05(const void* W, int ldw, const void* x, int l
                                     int* counters, int* err, int group_rows, int group_tokens, cudaStream_t stream) {
     using namespace prism::tc;
     if (M <= 0 || N <= 0) return 0;
+    const int glu_act = epi == 4 ? 1 : 0;
+    if (epi == 4) epi = EPI_SWIGLU;
     if (group_rows < 0 || group_rows % 128 || (group_rows > 0 && (group_tokens < M || epi == EPI_SWIGLU)))
         return (int)cudaErrorInvalidValue;
     if (!prism_gemm_tcgen05_supported(M, N, K) || ldw % 8 || ldx % 8 || ksplit < 1 || (ksplit > 1 && epi == EPI_SWIGLU) ||
@@ -291,7 +295,7 @@ PRISM_EXPORT int prism_gemm_tcgen05(const void* W, int ldw, const void* x, int l
     const int ntok = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     const long long w_rows = epi == EPI_SWIGLU ? 2LL * N : N;
     const int pair = epi == EPI_SWIGLU ? N : 0;
-#define ARGS W, ldw, w_rows, x, ldx, bias, bb, y, ldy, M, N, K, ksplit, pair, ws, counters, err, group_rows, group_tokens, stream
+#define ARGS W, ldw, w_rows, x, ldx, bias, bb, y, ldy, M, N, K, ksplit, pair, ws, counters, err, group_rows, group_tokens, glu_act, stream
 #define BY_N(E) (ntok == 16 ? launch<16, E>(ARGS) : ntok == 32 ? launch<32, E>(ARGS) : launch<64, E>(ARGS))
     switch (epi) {
         case EPI_BF16: return BY_N(EPI_BF16);

@@ -8,7 +8,8 @@ The design, as this file builds it from the parts:
   (entry 2i the sine, entry 2i + 1 the cosine of ``p 10000^(-2i/width)``);
 * every layer is a pre-norm block (RMS norms ``norm1`` / ``norm2``) whose mixer
   reads ``h + conv(h)``, a causal convolution over time of ``canon.taps`` taps
-  per channel (``l<i>.canon1``) beside a skip path; the feed-forward may be
+  per channel (``l<i>.canon1``) beside a skip path (a file without ``canon``
+  has no such convolution); the feed-forward may be
   absent; after it comes a per-layer token input: a slice of the row of
   ``side.embed`` that belongs to the token, gated by ``gelu_tanh(side.gate x)``,
   projected back (``side.proj``), RMS-normed with ``side.norm`` and added;
@@ -150,7 +151,7 @@ class TagelornConfig:
     width: int
     eps: float
     embedding_scale: float
-    taps: int
+    taps: Optional[int]           # None: the layers have no input convolution
     side_dim: Optional[int]           # None: no per-layer token input
     logit_softcap: Optional[float]
     layers: Tuple[TagelornLayer, ...]
@@ -162,7 +163,7 @@ class TagelornConfig:
         vocab, width = _pos_int(raw, "vocab", "the model"), _pos_int(raw, "width", "the model")
         eps = float(_need(_need(raw, "norm", "the model"), "eps", "norm"))
         scale = float((raw.get("embedding") or {}).get("scale", 1.0))
-        taps = _pos_int(_need(raw, "canon", "the model"), "taps", "canon")
+        taps = None if not raw.get("canon") else _pos_int(raw["canon"], "taps", "canon")     # no key: no input convolution
         side = raw.get("token_side")
         side_dim = None if not side else _pos_int(side, "dim", "token_side")
         cap = raw.get("logit_softcap")

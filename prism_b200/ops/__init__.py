@@ -256,6 +256,7 @@ def gemv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: to
 
 
 EPI_PARTIAL = 3
+EPI_GEGLU = 4          # the paired epilogue with the gate through gelu_tanh instead of silu
 _tc_err = {}
 
 
@@ -307,11 +308,11 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
     N = out.shape[-1]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
     assert x.stride(1) == 1 and w.stride(1) == 1 and out.is_contiguous()
-    assert w.shape[0] == (2 * N if epi == EPI_SWIGLU else N)
+    assert w.shape[0] == (2 * N if epi in (EPI_SWIGLU, EPI_GEGLU) else N)
     if epi == EPI_PARTIAL:
         assert out.dtype == torch.float32 and out.shape == (ksplit, M, N) and bias is None
     else:
-        assert out.shape == (M, N) and (ksplit == 1 or epi != EPI_SWIGLU)
+        assert out.shape == (M, N) and (ksplit == 1 or epi not in (EPI_SWIGLU, EPI_GEGLU))
         assert out.dtype == (torch.float32 if epi == EPI_F32 else torch.bfloat16)
     err = err if err is not None else _tc_err_word(x.device)
     ws = cnt = None
@@ -1413,6 +1414,10 @@ def feed_forward_glu(ctx, x: torch.Tensor, gate_up_w: torch.Tensor, down_w: torc
     takes the path with the activation in the product's epilogue (``feed_forward_swiglu``)."""
     if kind == "silu":
         return feed_forward_swiglu(ctx, x, gate_up_w, down_w)
+    if tc_gemm_ok(x, gate_up_w, TC_GEMM_MAX_M_SWIGLU):
+        act = ctx.alloc((x.shape[0], gate_up_w.shape[0] // 2), x.dtype)
+        gemm_tc(x, gate_up_w, None, act, EPI_GEGLU)        # gate/up product with the gated activation in its epilogue
+        return linear_delta(act, down_w)
     gu = linear(x, gate_up_w)
     act = ctx.alloc((x.shape[0], gate_up_w.shape[0] // 2), x.dtype)
     glu(gu, act, kind)
@@ -1950,13 +1955,14 @@ def _moe_route_place(L, logits, T, E, top, softmax, renorm, pad, counts, offs, s
 
 def moe_feed_forward(ctx, x: torch.Tensor, logits: torch.Tensor, gate_up_w: torch.Tensor, down_w: torch.Tensor, top: int,
                      softmax: bool = False, renorm: bool = False, scale_input: bool = True, act: str = "silu",
-                     gated: bool = True, choice: Optional[MoeChoice] = None) -> torch.Tensor:
+                     gated: bool = True, choice: Optional[MoeChoice] = None, extra_planes: int = 0) -> torch.Tensor:
     """Mixture of experts on the step's rows: ``x [T, W]`` (compute dtype), router ``logits [T, E]`` float32,
     ``gate_up_w [E, 2 F, W]`` (an expert's gate rows, then its up rows), ``down_w [E, W, F]``.  Each token takes the
     ``top`` experts with the largest scores (sigmoid of the logits, or their softmax); a choice's weight is its score
     (``renorm``: over the sum of the chosen) and multiplies the expert's input (``scale_input``) or its output.
     ``gated`` False: experts without a gate, ``down(act(up(a)))``, and ``gate_up_w`` is ``[E, F, W]``.  ``choice``: a
-    ``MoeChoice`` (correction, groups, weight scale).
+    ``MoeChoice`` (correction, groups, weight scale).  ``extra_planes``: the stack gets that many more planes after the
+    choices' for the caller to fill (a shared expert's result), so that nothing is copied together afterwards.
     Returns float32 ``[top, T, W]``: one plane per choice, which the next norm adds up.  The rows are sorted by
     expert on the device and run as grouped products; the host never learns the counts.  bf16 with rows of 16-byte
     multiples: tcgen05 tiles of one expert each (``csrc/moe_tcgen05.cu``); otherwise CUDA cores (``csrc/moe.cu``)."""
@@ -1991,7 +1997,7 @@ def moe_feed_forward(ctx, x: torch.Tensor, logits: torch.Tensor, gate_up_w: torc
         hidden = ctx.alloc((padded, F), x.dtype)
         _check(L.prism_moe_gemm_tcgen05(_ptr(xs), W, _ptr(gate_up_w), _ptr(offs), _ptr(counts), None, None, ntok, tiles, E, F, W,
                                         gt, MOE_ACTS[act], _ptr(hidden), F, _ptr(err), _stream()), "moe_gemm_tcgen05")
-        y = ctx.alloc((top, T, W), torch.float32)
+        y = ctx.alloc((top + extra_planes, T, W), torch.float32)
         _check(L.prism_moe_gemm_tcgen05(_ptr(hidden), F, _ptr(down_w), _ptr(offs), _ptr(counts), _ptr(row_dst),
                                         None if scale_input else _ptr(row_w), ntok, tiles, E, W, F, 0, 0, _ptr(y), W, _ptr(err),
                                         _stream()), "moe_gemm_tcgen05")
@@ -2006,7 +2012,7 @@ def moe_feed_forward(ctx, x: torch.Tensor, logits: torch.Tensor, gate_up_w: torc
     hidden = ctx.alloc((rows, F), x.dtype)
     _check(L.prism_moe_gemm(_ptr(x), x.stride(0), _ptr(gate_up_w), _dt(x), _ptr(offs), _ptr(row_tok), _ptr(row_w), _ptr(row_dst),
                             rows, E, F, W, 1, si, MOE_ACTS[act], _ptr(hidden), F, gt, _stream()), "moe_gemm")
-    y = ctx.alloc((top, T, W), torch.float32)
+    y = ctx.alloc((top + extra_planes, T, W), torch.float32)
     _check(L.prism_moe_gemm(_ptr(hidden), F, _ptr(down_w), _dt(x), _ptr(offs), _ptr(row_tok), _ptr(row_w), _ptr(row_dst),
                             rows, E, W, F, 0, si, 0, _ptr(y), W, 1, _stream()), "moe_gemm")
     return y

@@ -77,6 +77,12 @@ class ActMLP(FeedForward):
     def forward(self, ctx, x):
         return ops.feed_forward_act(ctx, x, self.w["up_w"], self.w["down_w"], self.activation)
 
+    def forward_to(self, ctx, x, out):
+        """The layer's result into ``out [T, hidden]`` (float32, contiguous): a plane of a stack that the next norm adds up."""
+        act = ctx.alloc((x.shape[0], self.intermediate_size), x.dtype)
+        ops.feed_forward_hidden(ctx, x, self.w["up_w"], self.activation, act)
+        ops.linear(act, self.w["down_w"], None, out=out)
+
 
 @register_part("feed_forward", "moe")
 class MixtureOfExperts(FeedForward):
@@ -91,8 +97,8 @@ class MixtureOfExperts(FeedForward):
     that is added to the scores for the choice only (the weights use the scores without it).  ``groups`` / ``keep``:
     the experts form ``groups`` equal groups of neighbours, a group's score is its largest choice score, and only
     experts of the best ``keep`` groups can be chosen.  ``weight_scale``: a constant on the weights; ``sum_eps``: added
-    to the sum that ``renorm`` divides by.  ``shared``: a feed-forward part that every token goes through and whose
-    result is added (its tensors under this part's prefix)."""
+    to the sum that ``renorm`` divides by.  ``shared``: a feed-forward part with ``forward_to`` (``mlp``) that every token
+    goes through and whose result is added (its tensors under this part's prefix)."""
 
     def __init__(self, hidden_size: int, intermediate_size: int, experts: int, top: int, softmax: bool = False,
                  renorm: bool = False, scale_input: bool = True, activation: str = "silu",
@@ -139,7 +145,7 @@ class MixtureOfExperts(FeedForward):
         logits = ops.linear(x, self.w["router_w"], None, out_dtype=ops.torch.float32)
         y = ops.moe_feed_forward(ctx, x, logits, self.w["gate_up_w"].view(E, (2 if self.gated else 1) * I, H),
                                  self.w["down_w"].view(E, H, I), self.top, self.softmax, self.renorm, self.scale_input,
-                                 self.activation, self.gated, self.choice)
-        if self.shared is None:
-            return y
-        return ops.stack_deltas(ctx, (y, self.shared.forward(ctx, x)))
+                                 self.activation, self.gated, self.choice, extra_planes=0 if self.shared is None else 1)
+        if self.shared is not None:
+            self.shared.forward_to(ctx, x, y[self.top])          # the shared expert's result is the stack's last plane
+        return y

@@ -42,7 +42,6 @@ def test_sizes_come_from_the_file_where_only_the_file_has_them():
 
 @pytest.mark.parametrize("edit, text", [
     (lambda r: r.pop("norm"), "norm"),
-    (lambda r: r.pop("canon"), "canon"),
     (lambda r: r["canon"].update(taps=0), "taps"),
     (lambda r: r.update(logit_softcap=-1.0), "logit_softcap"),
     (lambda r: r["layers"][0].update(type="conv"), "general_delta"),
@@ -92,6 +91,9 @@ def test_options_that_a_file_leaves_out():
     assert cfg.side_dim is None and cfg.logit_softcap is None
     names = [s.name for _, spec in mdl.named_params() for s in spec.sources]
     assert not [n for n in names if "side" in n or "norm2" in n or "mlp" in n]
+    raw.pop("canon")
+    names = [s.name for _, spec in build(raw)[1].named_params() for s in spec.sources]
+    assert not [n for n in names if "canon" in n] and len(build(raw)[1].cache_needs()[0].state_shape) == 3
     raw = model(40, 16, [layer("attention", attn(2, 1, 4), moe(8, 4, 2))], taps=2, side=3)
     names = [s.name for _, spec in build(raw)[1].named_params() for s in spec.sources]
     assert "side.embed" in names and "l0.side.proj" in names and "l0.mlp.correction" in names
@@ -128,8 +130,7 @@ def test_plain_window_keeps_the_first_positions():
 
 
 def test_plain_generalized_delta_rule_against_closed_forms():
-    """Without removal and with a constant decay the state is a decayed sum of outer products; with full removal along
-    a fixed unit key and no decay, writing the same key again replaces what was stored under it."""
+    """Without removal and with a constant decay the state is a decayed sum of outer products."""
     g = torch.Generator().manual_seed(2)
     T, W, d = 7, 5, 4
     h = torch.randn(T, W, generator=g).double()
