@@ -93,11 +93,22 @@ __global__ void gated_product_kernel(const T* __restrict__ x_in, long long x_str
 }
 
 template <typename T, int ACT>
-__global__ void glu_kernel(const T* __restrict__ gu_in, long long gs, T* __restrict__ out, long long os, int I) {
+__global__ void glu_kernel(const T* __restrict__ gu_in, long long gs, T* __restrict__ out, long long os, int I, int vec) {
     pdl_trigger();
     pdl_wait();
     const T* gu = pdl_fresh(gu_in) + (size_t)blockIdx.y * gs;
     T* o = out + (size_t)blockIdx.y * os;
+    if (vec) {                 // eight neighbouring columns a thread
+        const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+        if (c >= I) return;
+        float g[8], u[8];
+        load8(gu + c, g);
+        load8(gu + I + c, u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) g[k] = activate<ACT>(g[k]) * u[k];
+        store8(o + c, g);
+        return;
+    }
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < I; i += gridDim.x * blockDim.x)
         o[i] = from_float<T>(activate<ACT>(to_float(gu[i])) * to_float(gu[I + i]));
 }
@@ -164,10 +175,13 @@ PRISM_EXPORT int prism_glu(const void* gu, long long gu_stride, void* out, long 
                            int act, cudaStream_t stream) {
     if (rows <= 0 || I <= 0) return 0;
     if (rows > 65535 || (act != PRISM_ACT_SILU && act != PRISM_ACT_GELU_TANH)) return (int)cudaErrorInvalidValue;
-    dim3 grid((I + 255) / 256, rows);
+    const int esz = dtype == PRISM_DTYPE_BF16 ? 2 : 4;
+    const bool vec = I % 8 == 0 && gu_stride % 8 == 0 && out_stride % 8 == 0 && (uintptr_t)gu % (8 * esz) == 0 &&
+                     (uintptr_t)out % (8 * esz) == 0;
+    dim3 grid(((vec ? I / 8 : I) + 255) / 256, rows);
 #define PRISM_GLU(TT, A)                                                                                          \
     return (int)prism::launch_kernel(prism::glu_kernel<TT, A>, grid, dim3(256), 0, stream, (const TT*)gu, gu_stride, \
-                                     (TT*)out, out_stride, I)
+                                     (TT*)out, out_stride, I, vec ? 1 : 0)
     if (dtype == PRISM_DTYPE_BF16) {
         if (act == PRISM_ACT_SILU) PRISM_GLU(__nv_bfloat16, PRISM_ACT_SILU);
         PRISM_GLU(__nv_bfloat16, PRISM_ACT_GELU_TANH);

@@ -21,30 +21,77 @@ __device__ __forceinline__ float rg_gelu_tanh(float z) {
 
 // out[t][c] = bias[c] + sum_j taps[c][K-1-j] x[t-j][c] (+ x[t][c] with add_input: a convolution beside a skip path);
 // x [T, *] float32 with row stride xs; tail [slots, K-1, C]; out float32 or the compute dtype (rounded once).
-template <typename TO>
+// A CTA takes CONV_TOK consecutive tokens and blockDim.x * VEC channels; a thread owns VEC neighbouring channels (one
+// 128-bit load a row with VEC 4), keeps its taps in registers (up to CONV_MAX_TAPS; more are read as they are used) and
+// looks up a token's segment, place and slot once for all its taps.
+constexpr int CONV_TOK = 8;
+constexpr int CONV_MAX_TAPS = 8;
+template <typename TO, int VEC>
 __global__ void causal_conv_kernel(const float* __restrict__ x_in, long long xs, const void* __restrict__ taps, int taps_bf16,
                                    const void* __restrict__ bias, int bias_bf16, int K, int C, float* tail,
                                    const int* __restrict__ tok_seg, const int* __restrict__ seg_start,
                                    const int* __restrict__ slots, TO* __restrict__ out, long long os, int move_tail,
-                                   int add_input) {
+                                   int add_input, int T) {
     pdl_trigger();
+    const int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+    const bool live = c0 < C;
+    // taps and bias are constants of the model: in registers before the kernel before this one has ended
+    float tp[CONV_MAX_TAPS][VEC], bs[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) bs[v] = (live && bias != nullptr) ? load_param(bias, bias_bf16, c0 + v) : 0.f;
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; ++j)
+#pragma unroll
+        for (int v = 0; v < VEC; ++v)
+            tp[j][v] = (live && j < K) ? load_param(taps, taps_bf16, (size_t)(c0 + v) * K + (K - 1 - j)) : 0.f;      // lag j
     pdl_wait();
+    if (!live) return;
     const float* x = pdl_fresh(x_in);
-    const int t = blockIdx.x, seg = tok_seg[t];
-    const int i = t - seg_start[seg];
-    float* tl = tail + (size_t)slots[seg] * (K - 1) * C;
-    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
-        float acc = bias != nullptr ? load_param(bias, bias_bf16, c) : 0.f;
-        for (int j = K - 1; j >= 0; --j) {
+    const int t0 = blockIdx.x * CONV_TOK, t1 = min(T, t0 + CONV_TOK);
+    for (int t = t0; t < t1; ++t) {
+        const int seg = tok_seg[t];
+        const int i = t - seg_start[seg];
+        float* tl = tail + (size_t)slots[seg] * (K - 1) * C;
+        float acc[VEC], cur[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) acc[v] = bs[v];
+        auto load_row = [&](int j, float (&val)[VEC]) {          // the input j tokens back: this step's, or the tail's
             const int src = i - j;
-            const float v = src >= 0 ? x[(size_t)(t - j) * xs + c] : tl[(size_t)(K - 1 + src) * C + c];
-            acc += load_param(taps, taps_bf16, (size_t)c * K + (K - 1 - j)) * v;
+            const float* row = src >= 0 ? x + (size_t)(t - j) * xs + c0 : tl + (size_t)(K - 1 + src) * C + c0;
+            if (VEC == 4) {
+                const float4 q = *reinterpret_cast<const float4*>(row);
+                val[0] = q.x; val[1 % VEC] = q.y; val[2 % VEC] = q.z; val[3 % VEC] = q.w;
+            } else {
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) val[v] = row[v];
+            }
+        };
+        // oldest first, as the sum is written; lags beyond the taps held in registers read theirs as they go
+        for (int j = K - 1; j >= CONV_MAX_TAPS; --j) {
+            float val[VEC];
+            load_row(j, val);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) acc[v] += load_param(taps, taps_bf16, (size_t)(c0 + v) * K + (K - 1 - j)) * val[v];
         }
-        if (add_input) acc += x[(size_t)t * xs + c];
-        out[(size_t)t * os + c] = from_float<TO>(acc);
-        if (move_tail && K > 1) {          // one token per request: this thread is the only reader of its channel's tail
-            for (int r = 0; r + 2 < K; ++r) tl[(size_t)r * C + c] = tl[(size_t)(r + 1) * C + c];
-            tl[(size_t)(K - 2) * C + c] = x[(size_t)t * xs + c];
+#pragma unroll
+        for (int j = CONV_MAX_TAPS - 1; j >= 0; --j) {
+            if (j >= K) continue;
+            float val[VEC];
+            load_row(j, val);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) {
+                acc[v] += tp[j][v] * val[v];
+                if (j == 0) cur[v] = val[v];
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) out[(size_t)t * os + c0 + v] = from_float<TO>(add_input ? acc[v] + cur[v] : acc[v]);
+        if (move_tail && K > 1) {          // one token per request: this thread is the only reader of its channels' tail
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) {
+                for (int r = 0; r + 2 < K; ++r) tl[(size_t)r * C + c0 + v] = tl[(size_t)(r + 1) * C + c0 + v];
+                tl[(size_t)(K - 2) * C + c0 + v] = cur[v];
+            }
         }
     }
 }
@@ -264,18 +311,26 @@ PRISM_EXPORT int prism_causal_conv(const float* x, long long x_stride, const voi
                                    int bias_dtype, int K, int C, float* tail, const int* tok_seg, const int* seg_start,
                                    const int* slots, int T, void* out, int out_dtype, long long out_stride, int move_tail,
                                    int add_input, cudaStream_t stream) {
+    using namespace prism;
     if (T <= 0 || C <= 0) return 0;
     if (K < 1) return (int)cudaErrorInvalidValue;
-    const int threads = 128;
-    int gy = (C + threads - 1) / threads;
-    if (gy > 64) gy = 64;
-    if (out_dtype == PRISM_DTYPE_BF16)
-        return (int)prism::launch_kernel(prism::causal_conv_kernel<__nv_bfloat16>, dim3(T, gy), dim3(threads), 0, stream, x,
-                                         x_stride, taps, taps_dtype == PRISM_DTYPE_BF16, bias, bias_dtype == PRISM_DTYPE_BF16, K, C,
-                                         tail, tok_seg, seg_start, slots, (__nv_bfloat16*)out, out_stride, move_tail, add_input);
-    return (int)prism::launch_kernel(prism::causal_conv_kernel<float>, dim3(T, gy), dim3(threads), 0, stream, x, x_stride, taps,
-                                     taps_dtype == PRISM_DTYPE_BF16, bias, bias_dtype == PRISM_DTYPE_BF16, K, C, tail, tok_seg,
-                                     seg_start, slots, (float*)out, out_stride, move_tail, add_input);
+    // 128-bit loads where every row piece starts on 16 bytes
+    const bool vec = C % 4 == 0 && x_stride % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)tail % 16 == 0;
+    const int per = vec ? 4 : 1;
+    const int threads = C / per >= 128 ? 128 : (C / per >= 64 ? 64 : 32);
+    const dim3 grid((T + CONV_TOK - 1) / CONV_TOK, (C + threads * per - 1) / (threads * per));
+    if (grid.y > 65535) return (int)cudaErrorInvalidValue;
+    const int tb = taps_dtype == PRISM_DTYPE_BF16, bb = bias_dtype == PRISM_DTYPE_BF16;
+#define PRISM_CONV(TO, V)                                                                                               \
+    return (int)launch_kernel(causal_conv_kernel<TO, V>, grid, dim3(threads), 0, stream, x, x_stride, taps, tb, bias, bb, K, C, \
+                              tail, tok_seg, seg_start, slots, (TO*)out, out_stride, move_tail, add_input, T)
+    if (out_dtype == PRISM_DTYPE_BF16) {
+        if (vec) PRISM_CONV(__nv_bfloat16, 4);
+        PRISM_CONV(__nv_bfloat16, 1);
+    }
+    if (vec) PRISM_CONV(float, 4);
+    PRISM_CONV(float, 1);
+#undef PRISM_CONV
 }
 
 // u [T, blocks * bs] float32 (row stride u_stride); wr, wi [blocks, bs, bs] of w_dtype; br, bi [blocks * bs] of b_dtype;

@@ -195,6 +195,46 @@ __global__ void __launch_bounds__(1024) scale_add_rmsnorm_vec_kernel(float* __re
     }
 }
 
+// Residual add, RMSNorm and a short causal convolution beside a skip path in one launch, for a step in which every
+// request brings ONE token (all earlier inputs of the convolution are in the request's tail):
+//   residual[t] += sum_s delta[s, t];   h = rmsnorm(residual[t]) * w;
+//   out[t][c] = h[c] + sum_{j >= 1} taps[c][K-1-j] tail[slot][K-1-j][c] + taps[c][K-1] h[c];   tail moves up by h.
+// One block per token; a thread norms and convolves its own channels, so nothing but the sum of squares crosses threads.
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_conv_kernel(float* __restrict__ residual, const TD* __restrict__ delta_in, int nsplit,
+                                        size_t split_stride, const void* __restrict__ weight, int weight_bf16, float eps,
+                                        const void* __restrict__ taps, int taps_bf16, int K, float* tail,
+                                        const int* __restrict__ slots, TO* __restrict__ out, int H) {
+    pdl_trigger();
+    pdl_wait();
+    const TD* delta = pdl_fresh(delta_in);
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    float* res = residual + (size_t)t * H;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = res[c];
+        if (delta != nullptr) {
+            for (int s = 0; s < nsplit; ++s) v += to_float(delta[(size_t)s * split_stride + (size_t)t * H + c]);
+            res[c] = v;
+        }
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    float* tl = tail + (size_t)slots[t] * (K - 1) * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float h = res[c] * inv * load_param(weight, weight_bf16, c);
+        float acc = 0.f;
+        for (int j = K - 1; j >= 1; --j)               // oldest first
+            acc += load_param(taps, taps_bf16, (size_t)c * K + (K - 1 - j)) * tl[(size_t)(K - 1 - j) * H + c];
+        acc += load_param(taps, taps_bf16, (size_t)c * K + (K - 1)) * h;
+        out[(size_t)t * H + c] = from_float<TO>(acc + h);
+        for (int r = 0; r + 2 < K; ++r) tl[(size_t)r * H + c] = tl[(size_t)(r + 1) * H + c];
+        if (K > 1) tl[(size_t)(K - 2) * H + c] = h;
+    }
+}
+
 // The residual sum alone, for a sublayer that reads the stream itself rather than its norm:
 //   residual[r, :] += sum_s delta[s, r, :]   (float32, in place);   copy[r, :] = residual[r, :] in the compute dtype.
 template <typename TD, typename TO>
@@ -298,4 +338,27 @@ PRISM_EXPORT int prism_add_rows(float* residual, const void* delta, int delta_dt
     if (copy_dtype == PRISM_DTYPE_BF16) PRISM_AR(float, __nv_bfloat16);
     PRISM_AR(float, float);
 #undef PRISM_AR
+}
+
+// One token per request (T = segments): residual [T, H] float32 += delta; out [T, H] of out_dtype = h + conv(h) with h the
+// normed row, taps [H, K], tail [slots, K - 1, H] float32 (moved up by h), slots [T].
+PRISM_EXPORT int prism_add_rmsnorm_conv(float* residual, const void* delta, int delta_dtype, int nsplit, long long split_stride,
+                                        const void* weight, int weight_dtype, float eps, const void* taps, int taps_dtype, int K,
+                                        float* tail, const int* slots, void* out, int out_dtype, int T, int H,
+                                        cudaStream_t stream) {
+    if (T <= 0 || H <= 0) return 0;
+    if (K < 1) return (int)cudaErrorInvalidValue;
+    const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
+    const int wb = weight_dtype == PRISM_DTYPE_BF16, tb = taps_dtype == PRISM_DTYPE_BF16;
+#define PRISM_ANC(TD, TO)                                                                                                  \
+    return (int)prism::launch_kernel(prism::add_rmsnorm_conv_kernel<TD, TO>, dim3(T), dim3(threads), 0, stream, residual,   \
+                                     (const TD*)delta, nsplit, (size_t)split_stride, weight, wb, eps, taps, tb, K, tail, slots, \
+                                     (TO*)out, H)
+    if (delta_dtype == PRISM_DTYPE_BF16) {
+        if (out_dtype == PRISM_DTYPE_BF16) PRISM_ANC(__nv_bfloat16, __nv_bfloat16);
+        PRISM_ANC(__nv_bfloat16, float);
+    }
+    if (out_dtype == PRISM_DTYPE_BF16) PRISM_ANC(float, __nv_bfloat16);
+    PRISM_ANC(float, float);
+#undef PRISM_ANC
 }
