@@ -610,7 +610,8 @@ def tagelorn_kernel_numbers(s, pk, once=None):
         h32 = torch.randn(Tt, W, device=DEV)
         tail = torch.zeros(batch + 1, 3, W, device=DEV)
         h = torch.empty(Tt, W, device=DEV, dtype=torch.bfloat16)
-        run(f"input_conv_{label}", lambda: ops.causal_conv(h32, taps, None, tail, c, h, move_tail=q_len == 1, add_input=True), 0,
+        taps_t = taps.float().t().contiguous()
+        run(f"input_conv_{label}", lambda: ops.causal_conv(h32, taps, None, tail, c, h, move_tail=q_len == 1, add_input=True, taps_t=taps_t), 0,
             4 * Tt * W + 2 * Tt * W + (8 * 3 * batch * W if q_len == 1 else 0), fp32=True)
         d = torch.randn(Tt, W, device=DEV)
         x1 = torch.randn(Tt, W, device=DEV)

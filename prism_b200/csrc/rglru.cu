@@ -21,43 +21,30 @@ __device__ __forceinline__ float rg_gelu_tanh(float z) {
 
 // out[t][c] = bias[c] + sum_j taps[c][K-1-j] x[t-j][c] (+ x[t][c] with add_input: a convolution beside a skip path);
 // x [T, *] float32 with row stride xs; tail [slots, K-1, C]; out float32 or the compute dtype (rounded once).
-// A CTA takes CONV_TOK consecutive tokens and blockDim.x * VEC channels; a thread owns VEC neighbouring channels (one
-// 128-bit load a row with VEC 4), keeps its taps in registers (up to CONV_MAX_TAPS; more are read as they are used) and
-// looks up a token's segment, place and slot once for all its taps.
-constexpr int CONV_TOK = 8;
-constexpr int CONV_MAX_TAPS = 8;
+// taps_t (or null): the same taps as float32 [K, C], which the vector path reads 128 bits at a time.
+// One CTA per token: it looks up the token's segment, place and slot once, and its threads walk the channels VEC at a
+// time (one 128-bit load a row with VEC 4), the loads of one pass independent of the next pass's.
 template <typename TO, int VEC>
 __global__ void causal_conv_kernel(const float* __restrict__ x_in, long long xs, const void* __restrict__ taps, int taps_bf16,
                                    const void* __restrict__ bias, int bias_bf16, int K, int C, float* tail,
                                    const int* __restrict__ tok_seg, const int* __restrict__ seg_start,
                                    const int* __restrict__ slots, TO* __restrict__ out, long long os, int move_tail,
-                                   int add_input, int T) {
+                                   int add_input, const float* __restrict__ taps_t) {
     pdl_trigger();
-    const int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
-    const bool live = c0 < C;
-    // taps and bias are constants of the model: in registers before the kernel before this one has ended
-    float tp[CONV_MAX_TAPS][VEC], bs[VEC];
-#pragma unroll
-    for (int v = 0; v < VEC; ++v) bs[v] = (live && bias != nullptr) ? load_param(bias, bias_bf16, c0 + v) : 0.f;
-#pragma unroll
-    for (int j = 0; j < CONV_MAX_TAPS; ++j)
-#pragma unroll
-        for (int v = 0; v < VEC; ++v)
-            tp[j][v] = (live && j < K) ? load_param(taps, taps_bf16, (size_t)(c0 + v) * K + (K - 1 - j)) : 0.f;      // lag j
+    const int t = blockIdx.x, seg = tok_seg[t];        // the step's descriptor is complete before the step's first kernel
+    const int i = t - seg_start[seg];
+    float* tl = tail + (size_t)slots[seg] * (K - 1) * C;
     pdl_wait();
-    if (!live) return;
     const float* x = pdl_fresh(x_in);
-    const int t0 = blockIdx.x * CONV_TOK, t1 = min(T, t0 + CONV_TOK);
-    for (int t = t0; t < t1; ++t) {
-        const int seg = tok_seg[t];
-        const int i = t - seg_start[seg];
-        float* tl = tail + (size_t)slots[seg] * (K - 1) * C;
+#pragma unroll 2
+    for (int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * VEC; c0 < C; c0 += gridDim.y * blockDim.x * VEC) {
         float acc[VEC], cur[VEC];
 #pragma unroll
-        for (int v = 0; v < VEC; ++v) acc[v] = bs[v];
-        auto load_row = [&](int j, float (&val)[VEC]) {          // the input j tokens back: this step's, or the tail's
+        for (int v = 0; v < VEC; ++v) acc[v] = bias != nullptr ? load_param(bias, bias_bf16, c0 + v) : 0.f;
+        for (int j = K - 1; j >= 0; --j) {             // lag j: the input j tokens back; oldest first
             const int src = i - j;
             const float* row = src >= 0 ? x + (size_t)(t - j) * xs + c0 : tl + (size_t)(K - 1 + src) * C + c0;
+            float val[VEC];
             if (VEC == 4) {
                 const float4 q = *reinterpret_cast<const float4*>(row);
                 val[0] = q.x; val[1 % VEC] = q.y; val[2 % VEC] = q.z; val[3 % VEC] = q.w;
@@ -65,22 +52,17 @@ __global__ void causal_conv_kernel(const float* __restrict__ x_in, long long xs,
 #pragma unroll
                 for (int v = 0; v < VEC; ++v) val[v] = row[v];
             }
-        };
-        // oldest first, as the sum is written; lags beyond the taps held in registers read theirs as they go
-        for (int j = K - 1; j >= CONV_MAX_TAPS; --j) {
-            float val[VEC];
-            load_row(j, val);
+            float w[VEC];
+            if (VEC == 4 && taps_t != nullptr) {       // the taps turned to [K, C] float32: one 128-bit load a lag
+                const float4 q = *reinterpret_cast<const float4*>(taps_t + (size_t)(K - 1 - j) * C + c0);
+                w[0] = q.x; w[1 % VEC] = q.y; w[2 % VEC] = q.z; w[3 % VEC] = q.w;
+            } else {
 #pragma unroll
-            for (int v = 0; v < VEC; ++v) acc[v] += load_param(taps, taps_bf16, (size_t)(c0 + v) * K + (K - 1 - j)) * val[v];
-        }
-#pragma unroll
-        for (int j = CONV_MAX_TAPS - 1; j >= 0; --j) {
-            if (j >= K) continue;
-            float val[VEC];
-            load_row(j, val);
+                for (int v = 0; v < VEC; ++v) w[v] = load_param(taps, taps_bf16, (size_t)(c0 + v) * K + (K - 1 - j));
+            }
 #pragma unroll
             for (int v = 0; v < VEC; ++v) {
-                acc[v] += tp[j][v] * val[v];
+                acc[v] += w[v] * val[v];
                 if (j == 0) cur[v] = val[v];
             }
         }
@@ -310,20 +292,24 @@ __global__ void rglru_apply_kernel(const float* __restrict__ a_in, const float* 
 PRISM_EXPORT int prism_causal_conv(const float* x, long long x_stride, const void* taps, int taps_dtype, const void* bias,
                                    int bias_dtype, int K, int C, float* tail, const int* tok_seg, const int* seg_start,
                                    const int* slots, int T, void* out, int out_dtype, long long out_stride, int move_tail,
-                                   int add_input, cudaStream_t stream) {
+                                   int add_input, const float* taps_t, cudaStream_t stream) {
     using namespace prism;
     if (T <= 0 || C <= 0) return 0;
+    if (taps_t != nullptr && (uintptr_t)taps_t % 16 != 0) taps_t = nullptr;
     if (K < 1) return (int)cudaErrorInvalidValue;
     // 128-bit loads where every row piece starts on 16 bytes
     const bool vec = C % 4 == 0 && x_stride % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)tail % 16 == 0;
     const int per = vec ? 4 : 1;
-    const int threads = C / per >= 128 ? 128 : (C / per >= 64 ? 64 : 32);
-    const dim3 grid((T + CONV_TOK - 1) / CONV_TOK, (C + threads * per - 1) / (threads * per));
-    if (grid.y > 65535) return (int)cudaErrorInvalidValue;
+    const int groups = (C + per - 1) / per;
+    const int threads = groups >= 256 ? 256 : (groups >= 128 ? 128 : (groups >= 64 ? 64 : 32));
+    // a step of few tokens: several CTAs share a token's channels, so that the GPU is not left to a handful of CTAs
+    int gy = 1;
+    while (T * gy < 128 && gy * threads * 2 <= groups) gy *= 2;
+    const dim3 grid(T, gy);
     const int tb = taps_dtype == PRISM_DTYPE_BF16, bb = bias_dtype == PRISM_DTYPE_BF16;
 #define PRISM_CONV(TO, V)                                                                                               \
     return (int)launch_kernel(causal_conv_kernel<TO, V>, grid, dim3(threads), 0, stream, x, x_stride, taps, tb, bias, bb, K, C, \
-                              tail, tok_seg, seg_start, slots, (TO*)out, out_stride, move_tail, add_input, T)
+                              tail, tok_seg, seg_start, slots, (TO*)out, out_stride, move_tail, add_input, taps_t)
     if (out_dtype == PRISM_DTYPE_BF16) {
         if (vec) PRISM_CONV(__nv_bfloat16, 4);
         PRISM_CONV(__nv_bfloat16, 1);

@@ -116,7 +116,7 @@ class _Sig:
     prism_moe_gemm_tcgen05 = [_p, _ll, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _ll, _p, _p]
     prism_moe_gemm = [_p, _ll, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _ll, _i, _p]
     prism_hyper_norm = [_p, _ll, _p, _ll, _p, _i, _i, _ll, _p, _i, _p, _i, _p, _i, _i, _p, _i, _f, _i, _p, _i, _p, _i, _i, _p]
-    prism_causal_conv = [_p, _ll, _p, _i, _p, _i, _i, _i, _p, _p, _p, _p, _i, _p, _i, _ll, _i, _i, _p]
+    prism_causal_conv = [_p, _ll, _p, _i, _p, _i, _i, _i, _p, _p, _p, _p, _i, _p, _i, _ll, _i, _i, _p, _p]
     prism_block_gates = [_p, _ll, _p, _p, _i, _p, _p, _i, _p, _i, _f, _i, _i, _i, _p, _p, _ll, _p]
     prism_rglru_scan = [_p, _p, _ll, _p, _ll, _p, _p, _p, _i, _i, _i, _p, _i, _ll, _p]
     prism_cache_store = [_p, _ll, _p, _i, _i, _p, _ll, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p]
@@ -128,7 +128,7 @@ class _Sig:
     prism_gather_gate = [_p, _ll, _p, _p, _i, _ll, _i, _i, _p, _i, _ll, _i, _i, _i, _p, _p]
     prism_softcap = [_p, _ll, _f, _p]
     prism_add_rows = [_p, _p, _i, _i, _ll, _p, _i, _i, _i, _p]
-    prism_add_rmsnorm_conv = [_p, _p, _i, _i, _ll, _p, _i, _f, _p, _i, _i, _p, _p, _p, _i, _i, _i, _p]
+    prism_add_rmsnorm_conv = [_p, _p, _i, _i, _ll, _p, _i, _f, _p, _i, _i, _p, _p, _p, _i, _i, _i, _p, _p]
     prism_rms_rows = [_p, _ll, _p, _i, _f, _p, _ll, _i, _i, _i, _p]
     prism_attention_bf16_supported = [_i, _i, _i]
     prism_attention_decode_bf16 = [_p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f,
@@ -1411,11 +1411,14 @@ def add_rows(residual: torch.Tensor, delta: Optional[torch.Tensor], copy: Option
 
 
 def add_rmsnorm_conv(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
-                     taps: torch.Tensor, tail: torch.Tensor, slots: torch.Tensor, out: torch.Tensor):
+                     taps: torch.Tensor, tail: torch.Tensor, slots: torch.Tensor, out: torch.Tensor,
+                     taps_t: Optional[torch.Tensor] = None):
     """A step in which every request brings one token: ``residual += delta`` (as ``add_rmsnorm``), ``h = rmsnorm(residual)
     * weight``, ``out = h + conv(h)`` with the convolution's earlier inputs in ``tail [slots, K - 1, H]`` (float32; moved
-    up by h), all in one launch.  ``taps [H, K]``, ``slots`` int32 ``[T]``, ``out [T, H]`` float32 or the compute dtype."""
-    _cuda(residual, delta, weight, taps, tail, slots, out)
+    up by h), all in one launch.  ``taps [H, K]``, ``slots`` int32 ``[T]``, ``out [T, H]`` float32 or the compute dtype; ``taps_t``: the taps as
+    float32 ``[K, H]``."""
+    _cuda(residual, delta, weight, taps, tail, slots, out, taps_t)
+    assert taps_t is None or (taps_t.dtype == torch.float32 and taps_t.is_contiguous() and taps_t.shape == (taps.shape[1], taps.shape[0]))
     assert residual.dtype == torch.float32 and residual.is_contiguous() and out.is_contiguous()
     T, H = residual.shape
     K = taps.shape[1]
@@ -1428,7 +1431,7 @@ def add_rmsnorm_conv(residual: torch.Tensor, delta: Optional[torch.Tensor], weig
     assert slots.dtype == torch.int32 and slots.shape[0] >= T
     _check(lib().prism_add_rmsnorm_conv(_ptr(residual), _ptr(delta), F32 if delta is None else _dt(delta), nsplit, T * H,
                                         _ptr(weight), _dt(weight), float(eps), _ptr(taps), _dt(taps), K, _ptr(tail), _ptr(slots),
-                                        _ptr(out), _dt(out), T, H, _stream()), "add_rmsnorm_conv")
+                                        _ptr(out), _dt(out), T, H, _ptr(taps_t), _stream()), "add_rmsnorm_conv")
 
 
 def feed_forward_glu(ctx, x: torch.Tensor, gate_up_w: torch.Tensor, down_w: torch.Tensor, kind: str):
@@ -1866,13 +1869,15 @@ def hyper_norm(x: torch.Tensor, streams: int, x_out: Optional[torch.Tensor], del
 
 
 def causal_conv(x: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], tail: torch.Tensor, ctx, out: torch.Tensor,
-                move_tail: bool = False, add_input: bool = False):
+                move_tail: bool = False, add_input: bool = False, taps_t: Optional[torch.Tensor] = None):
     """``out[t, c] = bias[c] + sum_j taps[c, K-1-j] x[t-j, c]``: a short causal convolution over time per channel,
     float32; ``x [T, C]`` (row stride free), ``taps [C, K]`` (last column: the current token's), ``tail [slots, K - 1,
     C]`` the request's last inputs before this step.  ``move_tail``: every request brings one token, and the kernel
     moves the tail up itself (else ``state_tail`` follows).  ``add_input``: ``out = x + conv(x)``.  ``out``: float32
-    or the compute dtype (rounded once)."""
-    _cuda(x, taps, bias, tail, out)
+    or the compute dtype (rounded once).  ``taps_t``: the same taps as float32 ``[K, C]`` (made once by the caller), read
+    128 bits at a time where the sizes allow."""
+    _cuda(x, taps, bias, tail, out, taps_t)
+    assert taps_t is None or (taps_t.dtype == torch.float32 and taps_t.is_contiguous() and taps_t.shape == (taps.shape[1], taps.shape[0]))
     T = x.shape[0]
     C, K = taps.shape
     assert x.dtype == torch.float32 and x.stride(1) == 1 and x.shape[1] == C and taps.is_contiguous()
@@ -1881,7 +1886,7 @@ def causal_conv(x: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor
     assert bias is None or (bias.shape == (C,) and bias.is_contiguous())
     _check(lib().prism_causal_conv(_ptr(x), x.stride(0), _ptr(taps), _dt(taps), _ptr(bias), F32 if bias is None else _dt(bias),
                                    K, C, _ptr(tail), _ptr(ctx.tok_seg), _ptr(ctx.seg_start), _ptr(ctx.state_slots), T, _ptr(out),
-                                   _dt(out), out.stride(0), 1 if move_tail else 0, 1 if add_input else 0, _stream()), "causal_conv")
+                                   _dt(out), out.stride(0), 1 if move_tail else 0, 1 if add_input else 0, _ptr(taps_t), _stream()), "causal_conv")
 
 
 def block_gates(u: torch.Tensor, wr: torch.Tensor, wi: torch.Tensor, br: torch.Tensor, bi: torch.Tensor, lam: torch.Tensor,

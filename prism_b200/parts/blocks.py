@@ -83,7 +83,10 @@ class PreNormBlock(Block):
         return ps
 
     def on_bound(self):
-        self.no_tail = None
+        self.no_tail = self.taps_t = None
+        if self.taps is not None and self.w.get("conv_taps") is not None:
+            # the taps once more as float32 [K, width]: the kernels' neighbouring threads read neighbouring floats
+            self.taps_t = self.w["conv_taps"].float().t().contiguous()
         if self.taps == 1:
             self.no_tail = ops.torch.zeros((1, 0, self.hidden_size), dtype=ops.torch.float32, device=self.device)
 
@@ -100,11 +103,11 @@ class PreNormBlock(Block):
             tail = self.no_tail
         if ctx.decode_only and hasattr(self.mixer_norm, "forward_conv"):
             # one token per request: sum, norm, convolution and the tail's move in one launch
-            return self.mixer_norm.forward_conv(ctx, residual, delta, self.w["conv_taps"], tail), cache
+            return self.mixer_norm.forward_conv(ctx, residual, delta, self.w["conv_taps"], tail, self.taps_t), cache
         h32 = self.mixer_norm.forward(ctx, residual, delta, out_dtype=ops.torch.float32)
         h = ctx.alloc(tuple(h32.shape), ctx.dtype)
         single = ctx.decode_only          # one token per request: the kernel that reads the tail also moves it up
-        ops.causal_conv(h32, self.w["conv_taps"], None, tail, ctx, h, move_tail=single, add_input=True)
+        ops.causal_conv(h32, self.w["conv_taps"], None, tail, ctx, h, move_tail=single, add_input=True, taps_t=self.taps_t)
         if not single and self.taps > 1:
             ops.state_tail(h32, tail, ctx)
         return h, cache

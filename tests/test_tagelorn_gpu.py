@@ -83,7 +83,8 @@ def test_input_convolution_beside_the_skip_path_in_portions_and_token_by_token(C
             x = torch.cat([xs[s][a:a + n] for s, (a, n) in live]).to(DEV)
             out = torch.empty(x.shape[0], C, dtype=dtype, device=DEV)
             single = all(p[1] == 1 for _, p in live)
-            ops.causal_conv(x, taps.to(DEV), None, tail, ctx, out, move_tail=single, add_input=True)
+            ops.causal_conv(x, taps.to(DEV), None, tail, ctx, out, move_tail=single, add_input=True,
+                            taps_t=taps.t().contiguous().to(DEV) if k % 2 else None)
             if not single and K > 1:
                 ops.state_tail(x, tail, ctx)
             o = 0
@@ -115,7 +116,8 @@ def test_sum_norm_and_convolution_in_one_launch_for_single_tokens(H, K, dtype):
     for t in range(n):
         res = x[:, t].contiguous().to(DEV)
         out = torch.empty(S, H, dtype=dtype, device=DEV)
-        ops.add_rmsnorm_conv(res, d[:, t].transpose(0, 1).contiguous().to(DEV), w.to(DEV), 1e-5, taps.to(DEV), tail, slots, out)
+        ops.add_rmsnorm_conv(res, d[:, t].transpose(0, 1).contiguous().to(DEV), w.to(DEV), 1e-5, taps.to(DEV), tail, slots, out,
+                             taps.t().contiguous().to(DEV) if t % 2 else None)
         assert float((res.cpu() - (x[:, t] + d[:, t].sum(1))).abs().max()) <= 1e-5
         got[:, t] = out.float().cpu()
     for s in range(S):
