@@ -195,92 +195,6 @@ __global__ void __launch_bounds__(1024) scale_add_rmsnorm_vec_kernel(float* __re
     }
 }
 
-// Residual add, RMSNorm and a short causal convolution beside a skip path in one launch, for a step in which every
-// request brings ONE token (all earlier inputs of the convolution are in the request's tail):
-//   residual[t] += sum_s delta[s, t];   h = rmsnorm(residual[t]) * w;
-//   out[t][c] = h[c] + sum_{j >= 1} taps[c][K-1-j] tail[slot][K-1-j][c] + taps[c][K-1] h[c];   tail moves up by h.
-// One block per token; a thread norms and convolves its own channels, so nothing but the sum of squares crosses threads.
-template <typename TD, typename TO, int VEC>
-__global__ void add_rmsnorm_conv_kernel(float* __restrict__ residual, const TD* __restrict__ delta_in, int nsplit,
-                                        size_t split_stride, const void* __restrict__ weight, int weight_bf16, float eps,
-                                        const void* __restrict__ taps, int taps_bf16, int K, float* tail,
-                                        const int* __restrict__ slots, TO* __restrict__ out, int H,
-                                        const float* __restrict__ taps_t) {
-    pdl_trigger();
-    const int t = blockIdx.x;
-    float* tl = tail + (size_t)slots[t] * (K - 1) * H;          // the step's descriptor: complete before its first kernel
-    pdl_wait();
-    const TD* delta = pdl_fresh(delta_in);
-    __shared__ float scratch[33];
-    float* res = residual + (size_t)t * H;
-    float ss = 0.f;
-    for (int c = threadIdx.x * VEC; c < H; c += blockDim.x * VEC) {
-        float v[VEC];
-        if (VEC == 4) {
-            const float4 q = *reinterpret_cast<const float4*>(res + c);
-            v[0] = q.x; v[1 % VEC] = q.y; v[2 % VEC] = q.z; v[3 % VEC] = q.w;
-        } else {
-            v[0] = res[c];
-        }
-        if (delta != nullptr) {
-            for (int s = 0; s < nsplit; ++s)
-#pragma unroll
-                for (int k = 0; k < VEC; ++k) v[k] += to_float(delta[(size_t)s * split_stride + (size_t)t * H + c + k]);
-            if (VEC == 4) *reinterpret_cast<float4*>(res + c) = make_float4(v[0], v[1 % VEC], v[2 % VEC], v[3 % VEC]);
-            else res[c] = v[0];
-        }
-#pragma unroll
-        for (int k = 0; k < VEC; ++k) ss += v[k] * v[k];
-    }
-    ss = block_sum(ss, scratch);
-    const float inv = rsqrtf(ss / (float)H + eps);
-    for (int c = threadIdx.x * VEC; c < H; c += blockDim.x * VEC) {
-        float h[VEC], acc[VEC];
-#pragma unroll
-        for (int k = 0; k < VEC; ++k) {
-            h[k] = res[c + k] * inv * load_param(weight, weight_bf16, c + k);          // this thread wrote it: still in L1
-            acc[k] = 0.f;
-        }
-        for (int j = K - 1; j >= 1; --j) {             // oldest first; then the tail moves up by one row
-            float old[VEC];
-            if (VEC == 4) {
-                const float4 q = *reinterpret_cast<const float4*>(tl + (size_t)(K - 1 - j) * H + c);
-                old[0] = q.x; old[1 % VEC] = q.y; old[2 % VEC] = q.z; old[3 % VEC] = q.w;
-            } else {
-                old[0] = tl[(size_t)(K - 1 - j) * H + c];
-            }
-            float w[VEC];
-            if (VEC == 4 && taps_t != nullptr) {       // the taps turned to [K, H] float32: one 128-bit load a lag
-                const float4 q = *reinterpret_cast<const float4*>(taps_t + (size_t)(K - 1 - j) * H + c);
-                w[0] = q.x; w[1 % VEC] = q.y; w[2 % VEC] = q.z; w[3 % VEC] = q.w;
-            } else {
-#pragma unroll
-                for (int k = 0; k < VEC; ++k) w[k] = load_param(taps, taps_bf16, (size_t)(c + k) * K + (K - 1 - j));
-            }
-#pragma unroll
-            for (int k = 0; k < VEC; ++k) acc[k] += w[k] * old[k];
-            if (j < K - 1) {                           // row K-1-j becomes row K-2-j
-                if (VEC == 4) *reinterpret_cast<float4*>(tl + (size_t)(K - 2 - j) * H + c) = make_float4(old[0], old[1 % VEC], old[2 % VEC], old[3 % VEC]);
-                else tl[(size_t)(K - 2 - j) * H + c] = old[0];
-            }
-        }
-        float w0[VEC];
-        if (VEC == 4 && taps_t != nullptr) {
-            const float4 q = *reinterpret_cast<const float4*>(taps_t + (size_t)(K - 1) * H + c);
-            w0[0] = q.x; w0[1 % VEC] = q.y; w0[2 % VEC] = q.z; w0[3 % VEC] = q.w;
-        } else {
-#pragma unroll
-            for (int k = 0; k < VEC; ++k) w0[k] = load_param(taps, taps_bf16, (size_t)(c + k) * K + (K - 1));
-        }
-#pragma unroll
-        for (int k = 0; k < VEC; ++k) {
-            acc[k] += w0[k] * h[k];
-            out[(size_t)t * H + c + k] = from_float<TO>(acc[k] + h[k]);
-            if (K > 1) tl[(size_t)(K - 2) * H + c + k] = h[k];
-        }
-    }
-}
-
 // The residual sum alone, for a sublayer that reads the stream itself rather than its norm:
 //   residual[r, :] += sum_s delta[s, r, :]   (float32, in place);   copy[r, :] = residual[r, :] in the compute dtype.
 template <typename TD, typename TO>
@@ -384,36 +298,4 @@ PRISM_EXPORT int prism_add_rows(float* residual, const void* delta, int delta_dt
     if (copy_dtype == PRISM_DTYPE_BF16) PRISM_AR(float, __nv_bfloat16);
     PRISM_AR(float, float);
 #undef PRISM_AR
-}
-
-// One token per request (T = segments): residual [T, H] float32 += delta; out [T, H] of out_dtype = h + conv(h) with h the
-// normed row, taps [H, K], tail [slots, K - 1, H] float32 (moved up by h), slots [T]; taps_t (or null): the taps as
-// float32 [K, H] for 128-bit loads.
-PRISM_EXPORT int prism_add_rmsnorm_conv(float* residual, const void* delta, int delta_dtype, int nsplit, long long split_stride,
-                                        const void* weight, int weight_dtype, float eps, const void* taps, int taps_dtype, int K,
-                                        float* tail, const int* slots, void* out, int out_dtype, int T, int H,
-                                        const float* taps_t, cudaStream_t stream) {
-    if (T <= 0 || H <= 0) return 0;
-    if (taps_t != nullptr && (uintptr_t)taps_t % 16 != 0) taps_t = nullptr;
-    if (K < 1) return (int)cudaErrorInvalidValue;
-    const int threads = H >= 4096 ? 256 : 128;          // four channels a thread and pass
-    const int wb = weight_dtype == PRISM_DTYPE_BF16, tb = taps_dtype == PRISM_DTYPE_BF16;
-    const bool vec = H % 4 == 0 && (uintptr_t)residual % 16 == 0 && (uintptr_t)tail % 16 == 0;
-#define PRISM_ANC(TD, TO)                                                                                                  \
-    do {                                                                                                                   \
-        if (vec)                                                                                                           \
-            return (int)prism::launch_kernel(prism::add_rmsnorm_conv_kernel<TD, TO, 4>, dim3(T), dim3(threads), 0, stream, \
-                                             residual, (const TD*)delta, nsplit, (size_t)split_stride, weight, wb, eps, taps, \
-                                             tb, K, tail, slots, (TO*)out, H, taps_t);                                     \
-        return (int)prism::launch_kernel(prism::add_rmsnorm_conv_kernel<TD, TO, 1>, dim3(T), dim3(threads), 0, stream,      \
-                                         residual, (const TD*)delta, nsplit, (size_t)split_stride, weight, wb, eps, taps, tb, \
-                                         K, tail, slots, (TO*)out, H, taps_t);                                             \
-    } while (0)
-    if (delta_dtype == PRISM_DTYPE_BF16) {
-        if (out_dtype == PRISM_DTYPE_BF16) PRISM_ANC(__nv_bfloat16, __nv_bfloat16);
-        PRISM_ANC(__nv_bfloat16, float);
-    }
-    if (out_dtype == PRISM_DTYPE_BF16) PRISM_ANC(float, __nv_bfloat16);
-    PRISM_ANC(float, float);
-#undef PRISM_ANC
 }

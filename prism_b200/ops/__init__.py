@@ -128,7 +128,6 @@ class _Sig:
     prism_gather_gate = [_p, _ll, _p, _p, _i, _ll, _i, _i, _p, _i, _ll, _i, _i, _i, _p, _p]
     prism_softcap = [_p, _ll, _f, _p]
     prism_add_rows = [_p, _p, _i, _i, _ll, _p, _i, _i, _i, _p]
-    prism_add_rmsnorm_conv = [_p, _p, _i, _i, _ll, _p, _i, _f, _p, _i, _i, _p, _p, _p, _i, _i, _i, _p, _p]
     prism_rms_rows = [_p, _ll, _p, _i, _f, _p, _ll, _i, _i, _i, _p]
     prism_attention_bf16_supported = [_i, _i, _i]
     prism_attention_decode_bf16 = [_p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f,
@@ -1408,30 +1407,6 @@ def add_rows(residual: torch.Tensor, delta: Optional[torch.Tensor], copy: Option
         assert copy.shape == (T, H) and copy.is_contiguous()
     _check(lib().prism_add_rows(_ptr(residual), _ptr(delta), F32 if delta is None else _dt(delta), nsplit, T * H, _ptr(copy),
                                 F32 if copy is None else _dt(copy), T, H, _stream()), "add_rows")
-
-
-def add_rmsnorm_conv(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
-                     taps: torch.Tensor, tail: torch.Tensor, slots: torch.Tensor, out: torch.Tensor,
-                     taps_t: Optional[torch.Tensor] = None):
-    """A step in which every request brings one token: ``residual += delta`` (as ``add_rmsnorm``), ``h = rmsnorm(residual)
-    * weight``, ``out = h + conv(h)`` with the convolution's earlier inputs in ``tail [slots, K - 1, H]`` (float32; moved
-    up by h), all in one launch.  ``taps [H, K]``, ``slots`` int32 ``[T]``, ``out [T, H]`` float32 or the compute dtype; ``taps_t``: the taps as
-    float32 ``[K, H]``."""
-    _cuda(residual, delta, weight, taps, tail, slots, out, taps_t)
-    assert taps_t is None or (taps_t.dtype == torch.float32 and taps_t.is_contiguous() and taps_t.shape == (taps.shape[1], taps.shape[0]))
-    assert residual.dtype == torch.float32 and residual.is_contiguous() and out.is_contiguous()
-    T, H = residual.shape
-    K = taps.shape[1]
-    nsplit = 0
-    if delta is not None:
-        assert delta.is_contiguous() and delta.shape[-2:] == (T, H)
-        nsplit = 1 if delta.dim() == 2 else delta.shape[0]
-    assert out.shape == (T, H) and weight.shape == (H,) and taps.shape == (H, K) and taps.is_contiguous()
-    assert tail.dtype == torch.float32 and tail.is_contiguous() and tuple(tail.shape[1:]) == (max(K - 1, 0), H)
-    assert slots.dtype == torch.int32 and slots.shape[0] >= T
-    _check(lib().prism_add_rmsnorm_conv(_ptr(residual), _ptr(delta), F32 if delta is None else _dt(delta), nsplit, T * H,
-                                        _ptr(weight), _dt(weight), float(eps), _ptr(taps), _dt(taps), K, _ptr(tail), _ptr(slots),
-                                        _ptr(out), _dt(out), T, H, _ptr(taps_t), _stream()), "add_rmsnorm_conv")
 
 
 def feed_forward_glu(ctx, x: torch.Tensor, gate_up_w: torch.Tensor, down_w: torch.Tensor, kind: str):

@@ -101,9 +101,6 @@ class PreNormBlock(Block):
             cache = None if not rest else (rest[0] if len(rest) == 1 else tuple(rest))
         else:
             tail = self.no_tail
-        if ctx.decode_only and hasattr(self.mixer_norm, "forward_conv"):
-            # one token per request: sum, norm, convolution and the tail's move in one launch
-            return self.mixer_norm.forward_conv(ctx, residual, delta, self.w["conv_taps"], tail, self.taps_t), cache
         h32 = self.mixer_norm.forward(ctx, residual, delta, out_dtype=ops.torch.float32)
         h = ctx.alloc(tuple(h32.shape), ctx.dtype)
         single = ctx.decode_only          # one token per request: the kernel that reads the tail also moves it up

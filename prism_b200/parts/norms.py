@@ -33,13 +33,6 @@ class RMSNorm(Norm):
         ops.add_rmsnorm(residual, delta, self.w["weight"], self.eps, out, rows)
         return out
 
-    def forward_conv(self, ctx, residual, delta, taps, tail, taps_t=None):
-        """A step of single tokens: the residual sum, the norm and ``h + conv(h)`` (``taps [width, K]``, the convolution's
-        earlier inputs in ``tail``, moved up by h) in one launch; returns the mixer's input in the compute dtype."""
-        out = ctx.alloc((residual.shape[0], self.width), ctx.dtype)
-        ops.add_rmsnorm_conv(residual, delta, self.w["weight"], self.eps, taps, tail, ctx.state_slots, out, taps_t)
-        return out
-
     def forward_post(self, ctx, x, delta, alpha: float = 1.0):
         """Norm after the sum: ``x <- rmsnorm(alpha * x + delta) * weight`` in place on the float32 rows; returns
         the new rows in the compute dtype (``x`` itself in a float32 engine)."""

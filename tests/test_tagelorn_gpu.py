@@ -98,37 +98,6 @@ def test_input_convolution_beside_the_skip_path_in_portions_and_token_by_token(C
             assert float((tail[1] - 7.0).abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("H, K", [(5, 1), (40, 2), (320, 4), (1030, 3)])
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_sum_norm_and_convolution_in_one_launch_for_single_tokens(H, K, dtype):
-    """Three requests decode side by side for nine steps (slots 3, 0, 2; slot 1 is a neighbour's): residual sum, RMS norm
-    and ``h + conv(h)`` against the plain functions over each request's whole sequence."""
-    from prism_b200 import ops
-    g = torch.Generator().manual_seed(H + K)
-    n, S = 9, 3
-    x = torch.randn(S, n, H, generator=g)
-    d = torch.randn(S, n, 2, H, generator=g) * 0.3
-    w, taps = torch.randn(H, generator=g) * 0.2 + 1.0, torch.randn(H, K, generator=g) * 0.5
-    slots = torch.tensor([3, 0, 2], dtype=torch.int32, device=DEV)
-    tail = torch.zeros(4, max(K - 1, 0), H, device=DEV)
-    tail[1] = 5.0
-    got = torch.empty(S, n, H)
-    for t in range(n):
-        res = x[:, t].contiguous().to(DEV)
-        out = torch.empty(S, H, dtype=dtype, device=DEV)
-        ops.add_rmsnorm_conv(res, d[:, t].transpose(0, 1).contiguous().to(DEV), w.to(DEV), 1e-5, taps.to(DEV), tail, slots, out,
-                             taps.t().contiguous().to(DEV) if t % 2 else None)
-        assert float((res.cpu() - (x[:, t] + d[:, t].sum(1))).abs().max()) <= 1e-5
-        got[:, t] = out.float().cpu()
-    for s in range(S):
-        h = TP.rms((x[s] + d[s].sum(1)).double(), 1e-5) * w.double()
-        ref = TP.input_conv(h, taps.double())
-        tol = 1e-5 if dtype == torch.float32 else 2e-2
-        assert float((got[s].double() - ref).abs().max()) <= tol * max(1.0, float(ref.abs().max())), s
-    if K > 1:
-        assert float((tail[1] - 5.0).abs().max()) == 0.0
-
-
 def paged_case(segs, nkv, dk, dv, page_size, dtype, seed):
     """``segs``: (cached, new) per request.  Keys and values of every position in pages handed out in a scrambled
     order; returns the step's descriptor arrays, the planes, and the dense keys/values per request."""
