@@ -41,7 +41,6 @@ __global__ void causal_conv_kernel(const float* __restrict__ x_in, long long xs,
         float acc[VEC], cur[VEC];
 #pragma unroll
         for (int v = 0; v < VEC; ++v) acc[v] = bias != nullptr ? load_param(bias, bias_bf16, c0 + v) : 0.f;
-#pragma unroll 4
         for (int j = K - 1; j >= 0; --j) {             // lag j: the input j tokens back; oldest first
             const int src = i - j;
             const float* row = src >= 0 ? x + (size_t)(t - j) * xs + c0 : tl + (size_t)(K - 1 + src) * C + c0;
