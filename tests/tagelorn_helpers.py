@@ -92,9 +92,9 @@ CONFIG_D = model(90, 48, taps=5, side=8, scale=0.5, layers=[
 ])
 # E: a few hundred wide, sizes the tensor-core kernels take throughout but none a power of two times another; heads of 128;
 # inner widths that are no multiple of a k-block; every distance beyond the table; attention layers side by side
-CONFIG_E = model(500, 320, taps=3, side=24, softcap=15.0, scale=3.0, layers=[
-    layer("attention", attn(4, 2, 128, 64, scale=0.09, size=100, keep_first=3, bias_rows=20, bias_max=50), moe(72, 12, 4, count=4, keep=3, scale=2.0, shared=136)),
-    layer("attention", attn(6, 1, 64, 64, scale=0.125, size=48, keep_first=9, bias_rows=32, bias_max=240), dense(200)),
+CONFIG_E = model(500, 384, taps=3, side=16, softcap=20.0, scale=1.5, layers=[
+    layer("attention", attn(4, 2, 128, 64, scale=0.09, size=100, keep_first=3, bias_rows=20, bias_max=50), moe(72, 12, 3, count=6, keep=4, scale=2.0, shared=136)),
+    layer("attention", attn(6, 2, 64, 32, scale=0.11, size=48, keep_first=9, bias_rows=24, bias_max=180), dense(200)),
     layer("general_delta", delta(2, 128, 24), moe(40, 3, 3)),
 ])
 CONFIGS = {"A": (CONFIG_A, 11, 8), "B": (CONFIG_B, 12, 64), "C": (CONFIG_C, 13, 16), "D": (CONFIG_D, 14, 16), "E": (CONFIG_E, 15, 64)}

@@ -102,7 +102,7 @@ def test_options_that_a_file_leaves_out():
 
 def test_distance_rows():
     from prism_b200.parts.attention import distance_bucket
-    for rows, far in [(32, 240), (10, 30), (6, 11), (16, 64), (64, 512), (2, 3), (1, 1), (8, 4)]:
+    for rows, far in [(24, 200), (10, 30), (6, 11), (16, 64), (64, 512), (2, 3), (1, 1), (8, 4)]:
         got = [distance_bucket(n, rows, far) for n in range(3 * far + 5)]
         assert got == [TP.distance_bucket(n, rows, far) for n in range(3 * far + 5)]
         assert got[:rows // 2] == list(range(rows // 2))                      # a row each below half the table
