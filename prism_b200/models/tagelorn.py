@@ -86,10 +86,10 @@ class BiasedAttentionConfig:
     dim: int
     vdim: int
     scale: float
-    window: int
+    window: Optional[int]         # None: no window
     keep_first: int
-    bias_rows: int
-    bias_max: int
+    bias_rows: Optional[int]      # None: no bias by distance
+    bias_max: Optional[int]
 
 
 @dataclass(frozen=True)
@@ -183,14 +183,16 @@ class TagelornConfig:
                 if kvh < 1 or heads % kvh:
                     raise ConfigError(f"config.json: {mw}: heads ({heads}) not divisible by kv_heads ({kvh})")
                 dim = _pos_int(mx, "dim", mw)
-                mask = _need(mx, "mask", mw)
-                keep_first = int(mask.get("keep_first") or 0)
+                mask = mx.get("mask")                     # no mask: every earlier key is visible
+                window = None if not mask else _pos_int(mask, "size", mw + ".mask")
+                keep_first = 0 if not mask else int(mask.get("keep_first") or 0)
                 if keep_first < 0:
                     raise ConfigError(f"config.json: {mw}.mask.keep_first must not be negative")
-                mixer = BiasedAttentionConfig(
-                    heads, kvh, dim, int(mx.get("vdim") or dim), float(_need(mx, "scale", mw)), _pos_int(mask, "size", mw + ".mask"),
-                    keep_first, _from_shape(mx, "bias_rows", f"l{i}.mix.rel", tensor_shapes, mw, "the distance-bias table's"),
-                    _pos_int(mx, "bias_max", mw))
+                bias_max = None if mx.get("bias_max") is None else _pos_int(mx, "bias_max", mw)      # no key: no bias by distance
+                rows = None if bias_max is None else _from_shape(mx, "bias_rows", f"l{i}.mix.rel", tensor_shapes, mw,
+                                                                 "the distance-bias table's")
+                mixer = BiasedAttentionConfig(heads, kvh, dim, int(mx.get("vdim") or dim), float(_need(mx, "scale", mw)), window,
+                                              keep_first, rows, bias_max)
             elif kind == "general_delta":
                 mixer = GeneralDeltaConfig(_pos_int(mx, "heads", mw), _pos_int(mx, "dim", mw),
                                            _from_shape(mx, "decay_rank", f"l{i}.mix.w1", tensor_shapes, mw, "the decay's rank"))
@@ -213,7 +215,8 @@ def tagelorn_spec(cfg: TagelornConfig) -> ModelSpec:
             mixer = PartSpec("gqa_attention", dict(
                 hidden_size=W, num_heads=m.heads, num_kv_heads=m.kv_heads, head_dim=m.dim, v_head_dim=m.vdim,
                 qkv_bias=True, o_bias=False, scale=m.scale, window=m.window, keep_first=m.keep_first, sink=True,
-                qk_norm_eps=cfg.eps, qk_norm_weight=False, dist_bias=dict(rows=m.bias_rows, far=m.bias_max),
+                qk_norm_eps=cfg.eps, qk_norm_weight=False,
+                dist_bias=None if m.bias_max is None else dict(rows=m.bias_rows, far=m.bias_max),
                 names=dict(q="q", k="k", v="v", o="o", q_b="q.b", k_b="k.b", v_b="v.b", sink="sink", rel="rel")),
                 prefix=p + "mix.")
         else:

@@ -47,9 +47,7 @@ def test_sizes_come_from_the_file_where_only_the_file_has_them():
     (lambda r: r["layers"][0].update(type="conv"), "general_delta"),
     (lambda r: r["layers"][0]["mixer"].update(kv_heads=4), "divisible"),
     (lambda r: r["layers"][0]["mixer"].pop("scale"), "scale"),
-    (lambda r: r["layers"][0]["mixer"].pop("mask"), "mask"),
     (lambda r: r["layers"][0]["mixer"]["mask"].update(size=0), "size"),
-    (lambda r: r["layers"][0]["mixer"].pop("bias_max"), "bias_max"),
     (lambda r: r["layers"][1]["mixer"].pop("dim"), "dim"),
     (lambda r: r["layers"][0]["mlp"].update(kind="glu"), "dense"),
     (lambda r: r["layers"][1]["mlp"]["router"].update(top=5), "top"),
@@ -94,6 +92,12 @@ def test_options_that_a_file_leaves_out():
     raw.pop("canon")
     names = [s.name for _, spec in build(raw)[1].named_params() for s in spec.sources]
     assert not [n for n in names if "canon" in n] and len(build(raw)[1].cache_needs()[0].state_shape) == 3
+    raw = model(40, 16, [layer("attention", attn(2, 1, 4), None)])
+    for key in ("mask", "bias_max", "bias_rows"):
+        raw["layers"][0]["mixer"].pop(key)
+    cfg, mdl = build(raw)                                   # no mask: causal; no bias_max: no table of distances
+    assert cfg.layers[0].mixer.window is None and cfg.layers[0].mixer.bias_max is None
+    assert "l0.mix.rel" not in [s.name for _, spec in mdl.named_params() for s in spec.sources]
     raw = model(40, 16, [layer("attention", attn(2, 1, 4), moe(8, 4, 2))], taps=2, side=3)
     names = [s.name for _, spec in build(raw)[1].named_params() for s in spec.sources]
     assert "side.embed" in names and "l0.side.proj" in names and "l0.mlp.correction" in names
