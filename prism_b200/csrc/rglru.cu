@@ -78,6 +78,69 @@ __global__ void causal_conv_kernel(const float* __restrict__ x_in, long long xs,
     }
 }
 
+// The same convolution for portions of prompts where the sizes allow 128-bit accesses, the taps are given as float32
+// [K, C] and K <= CONVT_TAPS: a CTA takes CONVT_TOK consecutive tokens of the step.  Their segments, places and slots are
+// looked up side by side first; a thread then loads its four channels of all CONVT_TOK rows (independent loads) and of the
+// taps once, and serves every lag from those registers where the lag stays inside the tile and the token's segment, from
+// the rows before the tile or from the request's tail otherwise - in the order of the one-token kernel, so both give the
+// same sums.  A row is read from L2 about (CONVT_TOK + K - 1) / CONVT_TOK times instead of K times.
+constexpr int CONVT_TOK = 8;
+constexpr int CONVT_TAPS = 8;
+template <typename TO>
+__global__ void causal_conv_tile_kernel(const float* __restrict__ x_in, long long xs, const float* __restrict__ taps_t,
+                                        const void* __restrict__ bias, int bias_bf16, int K, int C, const float* tail,
+                                        const int* __restrict__ tok_seg, const int* __restrict__ seg_start,
+                                        const int* __restrict__ slots, TO* __restrict__ out, long long os, int add_input, int T) {
+    pdl_trigger();
+    __shared__ int s_place[CONVT_TOK], s_slot[CONVT_TOK];
+    const int t0 = blockIdx.x * CONVT_TOK;
+    if (threadIdx.x < CONVT_TOK) {                       // the step's descriptor is complete before the step's first kernel
+        const int t = t0 + threadIdx.x;
+        const int seg = t < T ? tok_seg[t] : 0;
+        s_place[threadIdx.x] = t < T ? t - seg_start[seg] : 0;
+        s_slot[threadIdx.x] = slots[seg];
+    }
+    __syncthreads();
+    pdl_wait();
+    const float* x = pdl_fresh(x_in);
+    for (int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * 4; c0 < C; c0 += gridDim.y * blockDim.x * 4) {
+        float4 w[CONVT_TAPS], xr[CONVT_TOK];
+#pragma unroll
+        for (int j = 0; j < CONVT_TAPS; ++j)            // w[j]: the tap of lag j
+            w[j] = j < K ? *reinterpret_cast<const float4*>(taps_t + (size_t)(K - 1 - j) * C + c0) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int tt = 0; tt < CONVT_TOK; ++tt)
+            xr[tt] = t0 + tt < T ? *reinterpret_cast<const float4*>(x + (size_t)(t0 + tt) * xs + c0) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (bias != nullptr)
+            b4 = make_float4(load_param(bias, bias_bf16, c0), load_param(bias, bias_bf16, c0 + 1), load_param(bias, bias_bf16, c0 + 2),
+                             load_param(bias, bias_bf16, c0 + 3));
+#pragma unroll
+        for (int tt = 0; tt < CONVT_TOK; ++tt) {
+            const int t = t0 + tt;
+            if (t >= T) break;
+            const int i = s_place[tt];
+            const float* tl = tail + (size_t)s_slot[tt] * (K - 1) * C + c0;
+            float4 acc = b4;
+#pragma unroll
+            for (int j = CONVT_TAPS - 1; j >= 0; --j) {   // oldest first
+                if (j >= K) continue;
+                float4 v;
+                if (j <= i) {
+                    if (tt - j >= 0) v = xr[tt - j >= 0 ? tt - j : 0];
+                    else v = *reinterpret_cast<const float4*>(x + (size_t)(t - j) * xs + c0);
+                } else {
+                    v = *reinterpret_cast<const float4*>(tl + (size_t)(K - 1 + i - j) * C);
+                }
+                acc.x += w[j].x * v.x; acc.y += w[j].y * v.y; acc.z += w[j].z * v.z; acc.w += w[j].w * v.w;
+            }
+            if (add_input) { acc.x += xr[tt].x; acc.y += xr[tt].y; acc.z += xr[tt].z; acc.w += xr[tt].w; }
+            TO* o = out + (size_t)t * os + c0;
+            o[0] = from_float<TO>(acc.x); o[1] = from_float<TO>(acc.y); o[2] = from_float<TO>(acc.z); o[3] = from_float<TO>(acc.w);
+        }
+    }
+}
+
 // Block b of channels [b bs, (b + 1) bs): r = sigmoid(Wr[b] u_b + br[b]), i = sigmoid(Wi[b] u_b + bi[b]);
 // a = exp(-c r softplus(lam)), g = sqrt(1 - a^2) i u.  Wr, Wi [blocks, bs, bs] ([out, in]); grid (bs tiles, token tiles,
 // blocks).  1 - a^2 is formed as -expm1(2 log a), which keeps its leading digits where a is close to 1.
@@ -307,6 +370,20 @@ PRISM_EXPORT int prism_causal_conv(const float* x, long long x_stride, const voi
     while (T * gy < 128 && gy * threads * 2 <= groups) gy *= 2;
     const dim3 grid(T, gy);
     const int tb = taps_dtype == PRISM_DTYPE_BF16, bb = bias_dtype == PRISM_DTYPE_BF16;
+    // portions of prompts: tiles of tokens whose rows and taps stay in registers
+    if (vec && !move_tail && taps_t != nullptr && K <= CONVT_TAPS && T >= 2 * CONVT_TOK && out_stride % 4 == 0) {
+        int ty = 1;
+        const int tiles = (T + CONVT_TOK - 1) / CONVT_TOK;
+        while (tiles * ty < 296 && ty * 128 * 2 <= groups) ty *= 2;
+        const dim3 tgrid(tiles, ty);
+        const int tthreads = groups / ty >= 128 ? 128 : (groups / ty >= 64 ? 64 : 32);
+        if (out_dtype == PRISM_DTYPE_BF16)
+            return (int)launch_kernel(causal_conv_tile_kernel<__nv_bfloat16>, tgrid, dim3(tthreads), 0, stream, x, x_stride, taps_t, bias,
+                                      bb, K, C, (const float*)tail, tok_seg, seg_start, slots, (__nv_bfloat16*)out, out_stride,
+                                      add_input, T);
+        return (int)launch_kernel(causal_conv_tile_kernel<float>, tgrid, dim3(tthreads), 0, stream, x, x_stride, taps_t, bias, bb, K, C,
+                                  (const float*)tail, tok_seg, seg_start, slots, (float*)out, out_stride, add_input, T);
+    }
 #define PRISM_CONV(TO, V)                                                                                               \
     return (int)launch_kernel(causal_conv_kernel<TO, V>, grid, dim3(threads), 0, stream, x, x_stride, taps, tb, bias, bb, K, C, \
                               tail, tok_seg, seg_start, slots, (TO*)out, out_stride, move_tail, add_input, taps_t)

@@ -64,18 +64,20 @@ def test_embedding_rows_scaled_with_sine_and_cosine_of_the_position(W):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_input_convolution_beside_the_skip_path_in_portions_and_token_by_token(C, K, dtype):
     """Two requests in slots 2 and 0 (slot 1 is a neighbour's and must stay), cut into portions shorter and longer than
-    the tail and into single tokens, against the plain convolution over the whole sequence."""
+    the tail and into single tokens, against the plain convolution over the whole sequence.  Steps of sixteen tokens and
+    more with the taps also given as float32 ``[K, C]`` take the kernel that works in tiles of tokens (a tile may hold the
+    end of one request and the start of the other)."""
     from prism_b200 import ops
     g = torch.Generator().manual_seed(C + K)
-    lens = (23, 9)
+    lens = (70, 33)
     xs = [torch.randn(n, C, generator=g) for n in lens]
     taps = torch.randn(C, K, generator=g) * 0.5
     refs = [TP.input_conv(x.double(), taps.double()) for x in xs]
-    for sizes in ((1,), (2, 7, 1, 3), (30,)):
+    for sizes in ((1,), (2, 7, 1, 3), (30,), (21, 2, 40)):
         tail = torch.zeros(3, max(K - 1, 0), C, device=DEV)
         tail[1] = 7.0
         got = [torch.empty(n, C) for n in lens]
-        for k, parts in enumerate(zip(*[cut(n, sizes) + [None] * 40 for n in lens])):
+        for k, parts in enumerate(zip(*[cut(n, sizes) + [None] * 80 for n in lens])):
             live = [(s, p) for s, p in enumerate(parts) if p is not None]
             if not live:
                 break
@@ -84,7 +86,7 @@ def test_input_convolution_beside_the_skip_path_in_portions_and_token_by_token(C
             out = torch.empty(x.shape[0], C, dtype=dtype, device=DEV)
             single = all(p[1] == 1 for _, p in live)
             ops.causal_conv(x, taps.to(DEV), None, tail, ctx, out, move_tail=single, add_input=True,
-                            taps_t=taps.t().contiguous().to(DEV) if k % 2 else None)
+                            taps_t=taps.t().contiguous().to(DEV) if k % 2 == 0 else None)
             if not single and K > 1:
                 ops.state_tail(x, tail, ctx)
             o = 0
